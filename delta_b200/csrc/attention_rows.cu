@@ -169,13 +169,16 @@ __global__ void rows_append_kernel(T* __restrict__ src, int src_stride, const in
 // value is the key].  One warp per head: the head is read into 32-bit shared memory, rotated on its first rot_dims
 // entries (table == nullptr: not), then divided by its root mean square over dk, sqrt(mean(x^2) + eps) (unit_norm == 0:
 // not), and rounded once.  q goes back in place, k to the cache row.  value_from_key: the value is the key as
-// projected, before rotation and norm (its first dv entries), so no v is read.
+// projected, before rotation and norm (its first dv entries), so no v is read.  bias (32 bit, laid out as a row of src) is
+// added to q, k and v as they are read.  q_norm / k_norm [dk]: before the rotation the head is RMS-normed with this
+// weight, x / sqrt(mean(x^2) + pre_eps) * w, the same weight for every head.
 template <typename T>
 __global__ void rows_append_unit_kernel(T* __restrict__ src, int src_stride, const int* __restrict__ tok_pos, const int* __restrict__ tok_row,
                                         const int* __restrict__ block_table, int max_pages, T* __restrict__ cache, int num_pages,
                                         const float* __restrict__ table, int table_positions, int rot_dims, int interleaved, int H,
                                         int KV, int dk, int dv, int ps, int row_width, int k_off, int v_off, int unit_norm, float eps,
-                                        int value_from_key, int* err) {
+                                        int value_from_key, const float* __restrict__ bias, const float* __restrict__ q_norm,
+                                        const float* __restrict__ k_norm, float pre_eps, int* err) {
   extern __shared__ float heads[];     // [warps][dk]
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const int pos = tok_pos[t], b = tok_row[t];
@@ -192,10 +195,18 @@ __global__ void rows_append_unit_kernel(T* __restrict__ src, int src_stride, con
     T* hp = base + (size_t)hs * dk;
     const bool is_key = hs >= H;
     T* crow = (is_key && at >= 0) ? cache + (((size_t)page * KV + (hs - H)) * ps + off) * row_width : nullptr;
+    float ss0 = 0.f;
     for (int i = lane; i < dk; i += 32) {
       const T raw = hp[i];
-      x[i] = to_f32<T>(raw);
-      if (crow != nullptr && value_from_key && i < dv) crow[v_off + i] = raw;
+      const float v = to_f32<T>(raw) + (bias != nullptr ? bias[(size_t)hs * dk + i] : 0.f);
+      x[i] = v;
+      ss0 += v * v;
+      if (crow != nullptr && value_from_key && i < dv) crow[v_off + i] = bias != nullptr ? from_f32<T>(v) : raw;
+    }
+    const float* pre_w = is_key ? k_norm : q_norm;
+    if (pre_w != nullptr) {      // the RMS norm with a weight, before the rotation
+      const float pre = 1.f / sqrtf(warp_sum(ss0) / (float)dk + pre_eps);
+      for (int i = lane; i < dk; i += 32) x[i] = x[i] * pre * pre_w[i];
     }
     __syncwarp();
     if (table != nullptr) {
@@ -228,7 +239,8 @@ __global__ void rows_append_unit_kernel(T* __restrict__ src, int src_stride, con
   const T* vsrc = base + (size_t)(H + KV) * dk;
   for (int idx = threadIdx.x; idx < KV * dv; idx += blockDim.x) {
     const int g = idx / dv, i = idx - g * dv;
-    cache[(((size_t)page * KV + g) * ps + off) * row_width + v_off + i] = vsrc[idx];
+    cache[(((size_t)page * KV + g) * ps + off) * row_width + v_off + i] =
+        bias != nullptr ? from_f32<T>(to_f32<T>(vsrc[idx]) + bias[(size_t)(H + KV) * dk + idx]) : vsrc[idx];
   }
 }
 
@@ -339,7 +351,8 @@ extern "C" int dk_rows_append(void* src, int src_stride, const int* tok_pos, con
 extern "C" int dk_rows_append_unit(void* src, int src_stride, const int* tok_pos, const int* tok_row, const int* block_table,
                                    int max_pages, void* cache, int num_pages, const float* table, int table_positions, int rot_dims,
                                    int interleaved, int T_, int H, int KV, int dk, int dv, int ps, int row_width, int k_off, int v_off,
-                                   int unit_norm, float eps, int value_from_key, int dtype, int* err, cudaStream_t stream) {
+                                   int unit_norm, float eps, int value_from_key, const float* bias, const float* q_norm,
+                                   const float* k_norm, float pre_eps, int dtype, int* err, cudaStream_t stream) {
   if (T_ == 0) return 0;
   DK_REQUIRE(T_ > 0 && H > 0 && KV > 0 && dk > 0 && dv > 0 && ps > 0, "rows_append_unit: bad sizes T=%d H=%d KV=%d dk=%d dv=%d ps=%d", T_, H, KV, dk, dv, ps);
   DK_REQUIRE(src_stride >= (H + KV) * dk + (value_from_key ? 0 : KV * dv), "rows_append_unit: rows of %d elements do not hold q, k and v", src_stride);
@@ -353,7 +366,7 @@ extern "C" int dk_rows_append_unit(void* src, int src_stride, const int* tok_pos
 #define LAUNCH(T)                                                                                                                 \
   rows_append_unit_kernel<T><<<T_, threads, smem, stream>>>((T*)src, src_stride, tok_pos, tok_row, block_table, max_pages, (T*)cache, \
                                                             num_pages, table, table_positions, rot_dims, interleaved, H, KV, dk, dv, \
-                                                            ps, row_width, k_off, v_off, unit_norm, eps, value_from_key, err)
+                                                            ps, row_width, k_off, v_off, unit_norm, eps, value_from_key, bias, q_norm, k_norm, pre_eps, err)
   if (dtype == DK_F32) LAUNCH(float);
   else if (dtype == DK_BF16) LAUNCH(__nv_bfloat16);
   else DK_REQUIRE(false, "rows_append_unit: unknown dtype %d", dtype);

@@ -452,6 +452,23 @@ __global__ void gated_rms_norm_kernel(const float* __restrict__ o, const T* __re
   }
 }
 
+// The same with the statistics taken per group of `group` consecutive entries (a head): one warp per group.
+template <typename T>
+__global__ void gated_group_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, int gate_stride,
+                                        const float* __restrict__ w, T* __restrict__ out, int n, int group, float eps) {
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const float* x = o + (size_t)t * n;
+  for (int g0 = (threadIdx.x >> 5) * group; g0 < n; g0 += warps * group) {
+    float ss = 0.f;
+    for (int i = lane; i < group; i += 32) ss += x[g0 + i] * x[g0 + i];
+    const float inv = 1.f / sqrtf(warp_sum(ss) / (float)group + eps);
+    for (int i = g0 + lane; i < g0 + group; i += 32) {
+      const float g = to_f32<T>(gate[(size_t)t * gate_stride + i]);
+      out[(size_t)t * n + i] = from_f32<T>(x[i] * inv * w[i] * (1.f / (1.f + expf(-g))));
+    }
+  }
+}
+
 size_t smem_floats(int dk, int dvs) { return (size_t)dk * dvs + 2 * (size_t)C * (dk + 1) + (size_t)C * dvs + C * (C + 1) + C + 1; }
 constexpr size_t SMEM_LIMIT = 200 * 1024;
 }  // namespace
@@ -492,11 +509,21 @@ extern "C" int dk_decay_attention(const void* src, int src_stride, int q_off, in
   return dk_check_launch("decay_attention");
 }
 
+// group: the entries whose root mean square is taken together (n: the whole row; a divisor of n: one head at a time)
 extern "C" int dk_gated_rms_norm(const float* o, const void* gate, int gate_stride, const float* w, void* out, int T_, int n, float eps,
-                                 int dtype, cudaStream_t stream) {
+                                 int group, int dtype, cudaStream_t stream) {
   if (T_ == 0) return 0;
   DK_REQUIRE(T_ > 0 && n > 0 && gate_stride >= n, "gated_rms_norm: bad sizes T=%d n=%d stride=%d", T_, n, gate_stride);
+  DK_REQUIRE(group > 0 && n % group == 0, "gated_rms_norm: groups of %d entries do not divide a row of %d", group, n);
   const int threads = n >= 2048 ? 256 : 128;
+  if (group != n) {
+    if (dtype == DK_F32)
+      gated_group_norm_kernel<float><<<T_, threads, 0, stream>>>(o, (const float*)gate, gate_stride, w, (float*)out, n, group, eps);
+    else if (dtype == DK_BF16)
+      gated_group_norm_kernel<__nv_bfloat16><<<T_, threads, 0, stream>>>(o, (const __nv_bfloat16*)gate, gate_stride, w, (__nv_bfloat16*)out, n, group, eps);
+    else DK_REQUIRE(false, "gated_rms_norm: unknown dtype %d", dtype);
+    return dk_check_launch("gated_rms_norm");
+  }
   if (dtype == DK_F32)
     gated_rms_norm_kernel<float><<<T_, threads, 0, stream>>>(o, (const float*)gate, gate_stride, w, (float*)out, n, eps);
   else if (dtype == DK_BF16)

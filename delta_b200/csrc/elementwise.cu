@@ -218,6 +218,53 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ ou
   }
 }
 
+// out[t][i] = a[t][i] * sigmoid(g[t * g_stride + i]): an output gate read from a wider row of products
+template <typename T>
+__global__ void sigmoid_gate_kernel(const T* __restrict__ a, const T* __restrict__ g, int g_stride, T* __restrict__ out, long long total, int n) {
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const long long t = idx / n;
+    const int i = (int)(idx - t * n);
+    const float gv = to_f32<T>(g[t * g_stride + i]);
+    out[idx] = from_f32<T>(to_f32<T>(a[idx]) * (1.f / (1.f + expf(-gv))));
+  }
+}
+
+extern "C" int dk_sigmoid_gate(const void* a, const void* g, int g_stride, void* out, int T_, int n, int dtype, cudaStream_t stream) {
+  if (T_ == 0) return 0;
+  DK_REQUIRE(T_ > 0 && n > 0 && g_stride >= n, "sigmoid_gate: bad sizes T=%d n=%d stride=%d", T_, n, g_stride);
+  const long long total = (long long)T_ * n;
+  long long blocks = (total + 255) / 256;
+  const long long most = (long long)dk_sm_count() * 16;
+  if (blocks > most) blocks = most;
+  if (dtype == DK_F32)
+    sigmoid_gate_kernel<float><<<(int)blocks, 256, 0, stream>>>((const float*)a, (const float*)g, g_stride, (float*)out, total, n);
+  else if (dtype == DK_BF16)
+    sigmoid_gate_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)g, g_stride,
+                                                                        (__nv_bfloat16*)out, total, n);
+  else DK_REQUIRE(false, "sigmoid_gate: unknown dtype %d", dtype);
+  return dk_check_launch("sigmoid_gate");
+}
+
+// y[t][i] += b[i], in place
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ y, const float* __restrict__ b, long long total, int n) {
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x)
+    y[idx] = from_f32<T>(to_f32<T>(y[idx]) + b[idx % n]);
+}
+
+extern "C" int dk_add_bias(void* y, const float* b, int T_, int n, int dtype, cudaStream_t stream) {
+  if (T_ == 0) return 0;
+  DK_REQUIRE(T_ > 0 && n > 0 && b != nullptr, "add_bias: bad sizes T=%d n=%d", T_, n);
+  const long long total = (long long)T_ * n;
+  long long blocks = (total + 255) / 256;
+  const long long most = (long long)dk_sm_count() * 16;
+  if (blocks > most) blocks = most;
+  if (dtype == DK_F32) add_bias_kernel<float><<<(int)blocks, 256, 0, stream>>>((float*)y, b, total, n);
+  else if (dtype == DK_BF16) add_bias_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>((__nv_bfloat16*)y, b, total, n);
+  else DK_REQUIRE(false, "add_bias: unknown dtype %d", dtype);
+  return dk_check_launch("add_bias");
+}
+
 extern "C" int dk_silu_mul(const void* gu, void* out, int T_, int I, int dtype, cudaStream_t stream) {
   if (T_ == 0) return 0;
   DK_REQUIRE(T_ > 0 && I > 0, "silu_mul: bad sizes T=%d I=%d", T_, I);

@@ -98,6 +98,48 @@ __device__ void pick_top(float* z, int E, int top, int* __restrict__ choice, flo
   }
 }
 
+// The choice by sigmoid scores: `pick` [E] holds score + correction and is used up, `score` [E] the scores s = sigmoid(z).  The
+// `top` largest of pick are chosen (the lowest index among equals); a chosen expert's weight is its score without the
+// correction, divided by the sum of the chosen scores (+ 1e-20), times `scale`.
+__device__ void pick_top_scored(float* pick, const float* score, int E, int top, float scale, int* __restrict__ choice,
+                                float* __restrict__ weight, int lane) {
+  float sum = 0.f, my_weight = 0.f;
+  int my_choice = -1;
+  for (int j = 0; j < top; ++j) {
+    float bv = -INFINITY;
+    int be = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = pick[e];
+      if (v > bv) {
+        bv = v;
+        be = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (ov > bv || (ov == bv && oe < be)) {
+        bv = ov;
+        be = oe;
+      }
+    }
+    const float sc = be < E ? score[be] : 0.f;
+    sum += sc;
+    if (lane == j) {
+      my_weight = sc;
+      my_choice = be < E ? be : -1;
+    }
+    __syncwarp();
+    if (lane == 0 && be < E) pick[be] = -INFINITY;
+    __syncwarp();
+  }
+  if (lane < top) {
+    choice[lane] = my_choice;
+    weight[lane] = my_weight / (sum + 1e-20f) * scale;
+  }
+}
+
 constexpr int ROUTER_WARPS = 8;
 
 // One warp per token; the logits are copied to the warp's shared memory first.
@@ -121,8 +163,9 @@ constexpr int ROUTER_ROWS = 8;      // rows of the matrix whose products a warp 
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 router_kernel(const T* __restrict__ x, const T* __restrict__ w, float* __restrict__ logits, int* __restrict__ choice,
-              float* __restrict__ weight, int T_, int d, int n_rows, int E, int top, int tpb) {
-  extern __shared__ float zs[];      // [tpb][n_rows]
+              float* __restrict__ weight, int T_, int d, int n_rows, int E, int top, int tpb, const float* __restrict__ correction,
+              float route_scale, int scored) {
+  extern __shared__ float zs[];      // [tpb][n_rows] (scored: and [tpb][E] behind them)
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int local = warp % tpb, share = warp / tpb, sharers = ROUTER_WARPS / tpb;
   const int t = blockIdx.x * tpb + local;
@@ -166,7 +209,19 @@ router_kernel(const T* __restrict__ x, const T* __restrict__ w, float* __restric
     }
   }
   __syncthreads();
-  if (live && share == 0) pick_top(z, E, top, choice + (size_t)t * top, weight + (size_t)t * top, lane);
+  if (!live || share != 0) return;
+  if (scored) {      // sigmoid scores; the correction joins the choice only
+    float* score = zs + (size_t)tpb * n_rows + (size_t)local * E;
+    for (int e = lane; e < E; e += 32) {
+      const float sc = 1.f / (1.f + expf(-z[e]));
+      score[e] = sc;
+      z[e] = sc + (correction != nullptr ? correction[e] : 0.f);
+    }
+    __syncwarp();
+    pick_top_scored(z, score, E, top, route_scale, choice + (size_t)t * top, weight + (size_t)t * top, lane);
+  } else {
+    pick_top(z, E, top, choice + (size_t)t * top, weight + (size_t)t * top, lane);
+  }
 }
 
 // One block.  sorted[p] = slot (token * top + choice) or -1; tile_expert[tile] = expert or -1.
@@ -201,12 +256,16 @@ __global__ void experts_align_kernel(const int* __restrict__ choice, int n_slots
   }
 }
 
-// ACT: A = tokens [*, K] gathered by sorted[p] / top, W = [E][2N][K] (gate rows, then up rows), out Y[p][N] of type T.
-// !ACT: A = Y [capacity, K] in sorted order, W = [E][N][K], out Z[slot][N] in float.
-template <typename T, bool ACT>
+// MODE 1 (gated): A = tokens [*, K] gathered by sorted[p] / top, W = [E][2N][K] (gate rows, then up rows), out Y[p][N] of type T.
+// MODE 2 (one branch): the same gather, W = [E][N][K], out Y[p][N] = relu(product)^2 of type T.
+// MODE 0: A = Y [capacity, K] in sorted order, W = [E][N][K], out Z[slot][N] in float.
+__device__ __forceinline__ float relu_squared(float x) { return x > 0.f ? x * x : 0.f; }
+
+template <typename T, int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS)
 experts_gemm_kernel(const T* __restrict__ A, const T* __restrict__ W, void* __restrict__ out, const int* __restrict__ sorted,
                     const int* __restrict__ tile_expert, int top, int N, int K, float limit, float alpha, float shift) {
+  constexpr bool ACT = MODE == 1, FIRST = MODE != 0;
   const int tile = blockIdx.y;
   const int e = tile_expert[tile];
   if (e < 0) return;
@@ -217,7 +276,7 @@ experts_gemm_kernel(const T* __restrict__ A, const T* __restrict__ W, void* __re
   const int tid = threadIdx.x;
   if (tid < TILE_M) {
     const int s = sorted[p0 + tid];
-    src_row[tid] = s < 0 ? -1 : (ACT ? s / top : p0 + tid);
+    src_row[tid] = s < 0 ? -1 : (FIRST ? s / top : p0 + tid);
   }
   __syncthreads();
   const T* We = W + (size_t)e * (ACT ? 2 : 1) * N * K;
@@ -274,6 +333,8 @@ experts_gemm_kernel(const T* __restrict__ A, const T* __restrict__ W, void* __re
         // the two products are rounded to the element type before the activation, as separate products would be
         const float g = to_f32<T>(from_f32<T>(acc[0][r][c])), u = to_f32<T>(from_f32<T>(acc[ACT ? 1 : 0][r][c]));
         ((T*)out)[(size_t)(p0 + lr) * N + n] = from_f32<T>(glu_value(g, u, limit, alpha, shift));
+      } else if (FIRST) {
+        ((T*)out)[(size_t)(p0 + lr) * N + n] = from_f32<T>(relu_squared(to_f32<T>(from_f32<T>(acc[0][r][c]))));
       } else {
         ((float*)out)[(size_t)s * N + n] = acc[0][r][c];
       }
@@ -291,11 +352,12 @@ constexpr int MMA_LD = MMA_BK + 8;      // padded row: ldmatrix reads eight rows
 constexpr int MMA_STAGES = 4;
 constexpr int MMA_SMEM = MMA_STAGES * (TILE_M + MMA_BN) * MMA_LD * 2;
 
-template <bool ACT>
+template <int MODE>
 __global__ void __launch_bounds__(256)
 experts_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W, void* __restrict__ out,
                         const int* __restrict__ sorted, const int* __restrict__ tile_expert, int top, int N, int K, float limit,
                         float alpha, float shift) {
+  constexpr bool ACT = MODE == 1, FIRST = MODE != 0;
   const int tile = blockIdx.y;
   const int e = tile_expert[tile];
   if (e < 0) return;
@@ -309,7 +371,7 @@ experts_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16
   const int n0 = blockIdx.x * cols, p0 = tile * TILE_M;
   if (tid < TILE_M) {
     const int s = sorted[p0 + tid];
-    src_row[tid] = s < 0 ? -1 : (ACT ? s / top : p0 + tid);
+    src_row[tid] = s < 0 ? -1 : (FIRST ? s / top : p0 + tid);
   }
   __syncthreads();
   const __nv_bfloat16* We = W + (size_t)e * (ACT ? 2 : 1) * N * K;
@@ -406,8 +468,14 @@ experts_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16
         for (int j = 0; j < 4; ++j) {
           const int n = n0 + wn * 32 + j * 8 + 2 * t4;
 #pragma unroll
-          for (int q = 0; q < 2; ++q)
-            if (n + q < N) ((float*)out)[(size_t)s * N + n + q] = acc[i][j][half * 2 + q];
+          for (int q = 0; q < 2; ++q) {
+            if (n + q >= N) continue;
+            if (FIRST)      // the product rounded to bfloat16 first, as a separate product would be
+              ((__nv_bfloat16*)out)[(size_t)(p0 + lr) * N + n + q] =
+                  __float2bfloat16_rn(relu_squared(__bfloat162float(__float2bfloat16_rn(acc[i][j][half * 2 + q]))));
+            else
+              ((float*)out)[(size_t)s * N + n + q] = acc[i][j][half * 2 + q];
+          }
         }
       }
     }
@@ -472,8 +540,10 @@ extern "C" int dk_router_topk(const float* logits, int ld, int* choice, float* w
   return dk_check_launch("router_topk");
 }
 
+// scored == 0: the softmax over the chosen logits.  scored == 1: sigmoid scores, `correction` [E] (or null) added for the choice
+// only, weights = chosen scores / their sum * route_scale.
 extern "C" int dk_router(const void* x, const void* w, float* logits, int* choice, float* weight, int T_, int d, int n_rows, int E, int top,
-                         int dtype, cudaStream_t stream) {
+                         const float* correction, float route_scale, int scored, int dtype, cudaStream_t stream) {
   if (T_ == 0) return 0;
   DK_REQUIRE(T_ > 0 && d > 0 && E > 0 && top > 0 && top <= E && n_rows >= E, "router: bad sizes T=%d d=%d E=%d top=%d rows=%d", T_, d, E, top, n_rows);
   DK_REQUIRE(top <= MAX_TOP, "router: %d choices a token are above the %d this kernel takes", top, MAX_TOP);
@@ -481,11 +551,11 @@ extern "C" int dk_router(const void* x, const void* w, float* logits, int* choic
   const int groups = (n_rows + ROUTER_ROWS - 1) / ROUTER_ROWS;
   int tpb = ROUTER_WARPS;
   while (tpb > 1 && (ROUTER_WARPS / tpb < groups) && (long long)T_ * (ROUTER_WARPS / tpb) < 16LL * dk_sm_count()) tpb /= 2;
-  const size_t smem = (size_t)tpb * n_rows * sizeof(float);
+  const size_t smem = (size_t)tpb * (n_rows + (scored ? E : 0)) * sizeof(float);
   DK_REQUIRE(smem <= 48 * 1024, "router: %d logits a token do not fit the shared memory", n_rows);
   const int blocks = (T_ + tpb - 1) / tpb;
   const bool vec = d % 8 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0;
-#define LAUNCH(T, V) router_kernel<T, V><<<blocks, ROUTER_WARPS * 32, smem, stream>>>((const T*)x, (const T*)w, logits, choice, weight, T_, d, n_rows, E, top, tpb)
+#define LAUNCH(T, V) router_kernel<T, V><<<blocks, ROUTER_WARPS * 32, smem, stream>>>((const T*)x, (const T*)w, logits, choice, weight, T_, d, n_rows, E, top, tpb, correction, route_scale, scored)
   if (dtype == DK_F32) {
     if (vec) LAUNCH(float, true);
     else LAUNCH(float, false);
@@ -512,33 +582,37 @@ extern "C" int dk_experts_gemm(const void* A, const void* W, void* out, const in
                                int N, int K, int act, float limit, float alpha, float shift, int dtype, cudaStream_t stream) {
   if (max_tiles == 0) return 0;
   DK_REQUIRE(max_tiles > 0 && N > 0 && K > 0 && top > 0, "experts_gemm: bad sizes tiles=%d N=%d K=%d top=%d", max_tiles, N, K, top);
+  DK_REQUIRE(act >= 0 && act <= 2, "experts_gemm: activation %d is not known (0 none, 1 gated, 2 relu squared)", act);
   DK_REQUIRE(max_tiles <= 65535, "experts_gemm: %d tiles are above the grid's limit", max_tiles);
   if (dtype == DK_BF16 && K % 8 == 0 && ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0) {
-    const int cols = act ? MMA_BN / 2 : MMA_BN;
+    const int cols = act == 1 ? MMA_BN / 2 : MMA_BN;
     const dim3 mgrid((N + cols - 1) / cols, max_tiles);
     static bool granted[DK_MAX_DEVICES] = {false};
     const int dev = dk_current_device();
     if (!granted[dev]) {
-      if (cudaFuncSetAttribute(experts_gemm_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, MMA_SMEM) != cudaSuccess ||
-          cudaFuncSetAttribute(experts_gemm_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, MMA_SMEM) != cudaSuccess) {
+      if (cudaFuncSetAttribute(experts_gemm_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, MMA_SMEM) != cudaSuccess ||
+          cudaFuncSetAttribute(experts_gemm_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, MMA_SMEM) != cudaSuccess ||
+          cudaFuncSetAttribute(experts_gemm_mma_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, MMA_SMEM) != cudaSuccess) {
         cudaGetLastError();
         DK_REQUIRE(false, "experts_gemm: %d bytes of shared memory were not granted", MMA_SMEM);
       }
       granted[dev] = true;
     }
-    if (act)
-      experts_gemm_mma_kernel<true><<<mgrid, 256, MMA_SMEM, stream>>>((const __nv_bfloat16*)A, (const __nv_bfloat16*)W, out, sorted, tile_expert,
-                                                                      top, N, K, limit, alpha, shift);
-    else
-      experts_gemm_mma_kernel<false><<<mgrid, 256, MMA_SMEM, stream>>>((const __nv_bfloat16*)A, (const __nv_bfloat16*)W, out, sorted, tile_expert,
-                                                                       top, N, K, limit, alpha, shift);
+#define MMA_LAUNCH(MODE)                                                                                                          \
+  experts_gemm_mma_kernel<MODE><<<mgrid, 256, MMA_SMEM, stream>>>((const __nv_bfloat16*)A, (const __nv_bfloat16*)W, out, sorted, tile_expert, \
+                                                                  top, N, K, limit, alpha, shift)
+    if (act == 1) MMA_LAUNCH(1);
+    else if (act == 2) MMA_LAUNCH(2);
+    else MMA_LAUNCH(0);
+#undef MMA_LAUNCH
     return dk_check_launch("experts_gemm");
   }
   const dim3 grid((N + TILE_N - 1) / TILE_N, max_tiles);
 #define LAUNCH(T)                                                                                                                  \
   do {                                                                                                                             \
-    if (act) experts_gemm_kernel<T, true><<<grid, GEMM_THREADS, 0, stream>>>((const T*)A, (const T*)W, out, sorted, tile_expert, top, N, K, limit, alpha, shift); \
-    else experts_gemm_kernel<T, false><<<grid, GEMM_THREADS, 0, stream>>>((const T*)A, (const T*)W, out, sorted, tile_expert, top, N, K, limit, alpha, shift);    \
+    if (act == 1) experts_gemm_kernel<T, 1><<<grid, GEMM_THREADS, 0, stream>>>((const T*)A, (const T*)W, out, sorted, tile_expert, top, N, K, limit, alpha, shift); \
+    else if (act == 2) experts_gemm_kernel<T, 2><<<grid, GEMM_THREADS, 0, stream>>>((const T*)A, (const T*)W, out, sorted, tile_expert, top, N, K, limit, alpha, shift); \
+    else experts_gemm_kernel<T, 0><<<grid, GEMM_THREADS, 0, stream>>>((const T*)A, (const T*)W, out, sorted, tile_expert, top, N, K, limit, alpha, shift);    \
   } while (0)
   if (dtype == DK_F32) LAUNCH(float);
   else if (dtype == DK_BF16) LAUNCH(__nv_bfloat16);

@@ -58,6 +58,7 @@ struct TcArgs {
   int expert_rows;
   int glu;
   float glu_limit, glu_alpha, glu_shift;
+  int relu_squared;  // the epilogue of a product of one branch: relu(y)^2 of the rounded product
 };
 
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
@@ -240,6 +241,12 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
       } else if (a.swiglu) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) y[i] = y[i] / (1.f + expf(-y[i])) * u[i];
+      } else if (a.relu_squared) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float v = fmaxf(__bfloat162float(__float2bfloat16_rn(y[i])), 0.f);
+          y[i] = v * v;
+        }
       }
       long long out_row = m0 + m;
       if (a.row_map != nullptr) out_row = a.row_map[m0 + m];
@@ -325,6 +332,7 @@ extern "C" int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N,
   a.row_map = nullptr;
   a.expert_rows = 0;
   a.glu = 0;
+  a.relu_squared = 0;
   a.glu_limit = a.glu_alpha = a.glu_shift = 0.f;
   a.out = out;
   a.err = err;
@@ -381,7 +389,7 @@ extern "C" int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N,
 // Grouped products for a mixture of experts: x [M, K] holds the rows of all experts in tiles of `tile_m` (128 or 256) rows,
 // tile c belonging to expert chunk_expert[c] (negative: no rows); W [E * expert_rows, K] holds the experts' matrices one
 // after the other, [gate (n) | up (n)] rows each when `glu`, else n rows.  out[row_map ? row_map[r] : r][0..n) for every row
-// r of x (rows mapped to a negative number are not stored).  One block per (128 rows of an expert's matrix, tile of x).
+// r of x (rows mapped to a negative number are not stored).  `glu` 2: n rows each and the epilogue relu(y)^2.  One block per (128 rows of an expert's matrix, tile of x).
 extern "C" int dk_experts_gemm_tc_supported(int n, int K, int glu) {
   return dk_gemm_tc_supported(128, glu ? 2 * n : n, K, glu);
 }
@@ -390,6 +398,8 @@ extern "C" int dk_experts_gemm_tc(const void* x, const void* W, void* out, const
                                   int tile_m, int n, int K, int E, int ldc, int out_dtype, int glu, float limit, float alpha,
                                   float shift, int* err, cudaStream_t stream) {
   if (M == 0) return 0;
+  const int relu_squared = glu == 2;      // glu: 0 the plain product, 1 the gated activation, 2 one branch through relu(y)^2
+  glu = glu == 1;
   DK_REQUIRE(tile_m == 128 || tile_m == 256, "experts_gemm_tc: tiles of 128 or 256 rows, got %d", tile_m);
   DK_REQUIRE(M > 0 && M % tile_m == 0 && E > 0, "experts_gemm_tc: %d rows are no whole tiles of %d", M, tile_m);
   DK_REQUIRE(dk_experts_gemm_tc_supported(n, K, glu), "experts_gemm_tc: sizes not taken: n=%d K=%d glu=%d", n, K, glu);
@@ -402,6 +412,7 @@ extern "C" int dk_experts_gemm_tc(const void* x, const void* W, void* out, const
   a.row_map = row_map;
   a.expert_rows = glu ? 2 * n : n;
   a.glu = glu;
+  a.relu_squared = relu_squared;
   a.glu_limit = limit; a.glu_alpha = alpha; a.glu_shift = shift;
   a.out = out;
   a.err = err;

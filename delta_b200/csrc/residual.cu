@@ -96,7 +96,56 @@ __global__ void residual_norm_kernel(float* __restrict__ X, const T* __restrict_
   for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_f32<TO>((xs[i] - mean) * inv * w[i]);
 }
 
+// out = factor * sum over the branches k of  rms_norm(y_k + b_k) * w_k : sublayers that run side by side, each normed over the
+// width with its own weight before they are summed.  One block per token, all in 32 bit.
+__global__ void normed_sum_kernel(const float* __restrict__ y1, const float* __restrict__ b1, const float* __restrict__ w1,
+                                  const float* __restrict__ y2, const float* __restrict__ b2, const float* __restrict__ w2,
+                                  float* __restrict__ out, int d, float eps, float factor) {
+  extern __shared__ __align__(16) float xs[];   // 2 d floats + 33
+  float* scratch = xs + 2 * d;
+  const size_t at = (size_t)blockIdx.x * d;
+  float s1 = 0.f, s2 = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float a = y1[at + i] + (b1 ? b1[i] : 0.f);
+    const float b = y2 ? y2[at + i] + (b2 ? b2[i] : 0.f) : 0.f;
+    xs[i] = a;
+    xs[d + i] = b;
+    s1 += a * a;
+    s2 += b * b;
+  }
+  s1 = block_sum(s1, scratch);
+  s2 = block_sum(s2, scratch);
+  const float i1 = 1.f / sqrtf(s1 / (float)d + eps), i2 = 1.f / sqrtf(s2 / (float)d + eps);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v = xs[i] * i1 * w1[i];
+    if (y2) v += xs[d + i] * i2 * w2[i];
+    out[at + i] = factor * v;
+  }
+}
+
 }  // namespace
+
+extern "C" int dk_normed_sum(const float* y1, const float* b1, const float* w1, const float* y2, const float* b2, const float* w2,
+                             float* out, int T_, int d, float eps, float factor, cudaStream_t stream) {
+  if (T_ == 0) return 0;
+  DK_REQUIRE(T_ > 0 && d > 0 && d <= 12000, "normed_sum: bad sizes T=%d d=%d (width up to 12000)", T_, d);
+  DK_REQUIRE(y1 != nullptr && w1 != nullptr && (y2 == nullptr || w2 != nullptr), "normed_sum: a branch without its weight");
+  const int threads = d >= 4096 ? 512 : (d >= 1024 ? 256 : 128);
+  const size_t smem = (size_t)(2 * d + 36) * sizeof(float);
+  if (smem > 48 * 1024) {
+    static bool granted[DK_MAX_DEVICES] = {false};
+    const int dev = dk_current_device();
+    if (!granted[dev]) {
+      if (cudaFuncSetAttribute(normed_sum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (2 * 12000 + 36) * 4) != cudaSuccess) {
+        cudaGetLastError();
+        DK_REQUIRE(false, "normed_sum: %zu bytes of shared memory were not granted", smem);
+      }
+      granted[dev] = true;
+    }
+  }
+  normed_sum_kernel<<<T_, threads, smem, stream>>>(y1, b1, w1, y2, b2, w2, out, d, eps, factor);
+  return dk_check_launch("normed_sum");
+}
 
 extern "C" int dk_embedding_pair(const int* tokens, const int* tok_row, const int* tok_pos, const int* row_q_start, const int* row_slot,
                                  int* prev_state, const void* table, float scale, const void* pair_table, long long buckets,
@@ -140,6 +189,7 @@ extern "C" int dk_residual_norm(float* X, const void* y1, const void* y2, const 
   if (y_dtype == DK_F32 && out_dtype == DK_F32) LAUNCH(float, float);
   else if (y_dtype == DK_BF16 && out_dtype == DK_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
   else if (y_dtype == DK_BF16 && out_dtype == DK_F32) LAUNCH(__nv_bfloat16, float);
+  else if (y_dtype == DK_F32 && out_dtype == DK_BF16) LAUNCH(float, __nv_bfloat16);
   else DK_REQUIRE(false, "residual_norm: unsupported dtypes y=%d out=%d", y_dtype, out_dtype);
 #undef LAUNCH
   return dk_check_launch("residual_norm");

@@ -20,7 +20,8 @@ constexpr int MAX_TAPS = 16;
 template <typename T>
 __global__ void conv_silu_kernel(const T* __restrict__ xin, int in_stride, const float* __restrict__ w, const float* __restrict__ bias,
                                  const float* __restrict__ conv_state, T* __restrict__ out, const int* __restrict__ tok_row,
-                                 const int* __restrict__ row_slot, const int* __restrict__ row_q_start, int C, int taps) {
+                                 const int* __restrict__ row_slot, const int* __restrict__ row_q_start, int C, int taps,
+                                 const float* __restrict__ in_bias, int act) {
   const int t = blockIdx.x;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= C) return;
@@ -29,19 +30,20 @@ __global__ void conv_silu_kernel(const T* __restrict__ xin, int in_stride, const
   const int i = t - q0;
   const float* st = conv_state + (size_t)row_slot[row] * (taps - 1) * C;
   float acc = bias ? bias[c] : 0.f;
+  const float ib = in_bias ? in_bias[c] : 0.f;      // a bias of the inputs themselves (the state holds it already)
   for (int j = 0; j < taps; ++j) {
     const int k = i - (taps - 1) + j;     // index among the row's tokens of this step; negative: before it
-    const float v = k >= 0 ? to_f32<T>(xin[(size_t)(q0 + k) * in_stride + c]) : st[(size_t)(taps - 1 + k) * C + c];
+    const float v = k >= 0 ? to_f32<T>(xin[(size_t)(q0 + k) * in_stride + c]) + ib : st[(size_t)(taps - 1 + k) * C + c];
     acc = fmaf(w[(size_t)c * taps + j], v, acc);
   }
-  out[(size_t)t * C + c] = from_f32<T>(acc / (1.f + expf(-acc)));
+  out[(size_t)t * C + c] = from_f32<T>(act ? acc / (1.f + expf(-acc)) : acc);
 }
 
 // grid (rows, ceil(C / blockDim)); one thread per (row, channel) reads what it needs, then writes
 template <typename T>
 __global__ void conv_state_kernel(const T* __restrict__ xin, int in_stride, float* __restrict__ conv_state,
                                   const int* __restrict__ row_slot, const int* __restrict__ row_q_start,
-                                  const int* __restrict__ row_q_len, int C, int taps) {
+                                  const int* __restrict__ row_q_len, int C, int taps, const float* __restrict__ in_bias) {
   const int row = blockIdx.x;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= C) return;
@@ -52,7 +54,7 @@ __global__ void conv_state_kernel(const T* __restrict__ xin, int in_stride, floa
   for (int j = 0; j < MAX_TAPS; ++j) {
     if (j < taps - 1) {
       const int k = L - (taps - 1) + j;
-      v[j] = k >= 0 ? to_f32<T>(xin[(size_t)(q0 + k) * in_stride + c]) : st[(size_t)(taps - 1 + k) * C + c];
+      v[j] = k >= 0 ? to_f32<T>(xin[(size_t)(q0 + k) * in_stride + c]) + (in_bias ? in_bias[c] : 0.f) : st[(size_t)(taps - 1 + k) * C + c];
     }
   }
 #pragma unroll
@@ -195,7 +197,9 @@ __global__ void scan_combine_kernel(const float* __restrict__ A_log, float* __re
 
 extern "C" int dk_conv_silu(const void* xin, int in_stride, const float* w, const float* bias, float* conv_state, void* out,
                             const int* tok_row, const int* row_slot, const int* row_q_start, const int* row_q_len, int T_,
-                            int rows, int C, int taps, int dtype, cudaStream_t stream) {
+                            int rows, int C, int taps, const float* in_bias, int act, int dtype, cudaStream_t stream) {
+  // in_bias [C] (or null) is added to every input as it is read, not to the zeros before a request's first token;
+  // act 1: silu behind the convolution, 0: none
   if (T_ == 0) return 0;
   DK_REQUIRE(T_ > 0 && rows > 0 && C > 0 && in_stride >= C, "conv_silu: bad sizes T=%d rows=%d C=%d stride=%d", T_, rows, C, in_stride);
   DK_REQUIRE(taps >= 1 && taps <= MAX_TAPS, "conv_silu: %d taps; this kernel takes 1 to %d", taps, MAX_TAPS);
@@ -205,15 +209,15 @@ extern "C" int dk_conv_silu(const void* xin, int in_stride, const float* w, cons
   DK_REQUIRE(g1.y <= 65535, "conv_silu: too many channels");
   if (dtype == DK_F32) {
     conv_silu_kernel<float><<<g1, threads, 0, stream>>>((const float*)xin, in_stride, w, bias, conv_state, (float*)out, tok_row,
-                                                        row_slot, row_q_start, C, taps);
+                                                        row_slot, row_q_start, C, taps, in_bias, act);
     if (taps > 1)
-      conv_state_kernel<float><<<g2, threads, 0, stream>>>((const float*)xin, in_stride, conv_state, row_slot, row_q_start, row_q_len, C, taps);
+      conv_state_kernel<float><<<g2, threads, 0, stream>>>((const float*)xin, in_stride, conv_state, row_slot, row_q_start, row_q_len, C, taps, in_bias);
   } else {
     conv_silu_kernel<__nv_bfloat16><<<g1, threads, 0, stream>>>((const __nv_bfloat16*)xin, in_stride, w, bias, conv_state,
-                                                                (__nv_bfloat16*)out, tok_row, row_slot, row_q_start, C, taps);
+                                                                (__nv_bfloat16*)out, tok_row, row_slot, row_q_start, C, taps, in_bias, act);
     if (taps > 1)
       conv_state_kernel<__nv_bfloat16><<<g2, threads, 0, stream>>>((const __nv_bfloat16*)xin, in_stride, conv_state, row_slot,
-                                                                   row_q_start, row_q_len, C, taps);
+                                                                   row_q_start, row_q_len, C, taps, in_bias);
   }
   return dk_check_launch("conv_silu");
 }

@@ -54,7 +54,7 @@ _SIGNATURES = {
     "dk_stream_norm": [P, P, P, P, P, P, P, P, I, I, I, F, I, I, I, P],
     "dk_activation": [P, P, L, I, I, P],
     "dk_softcap": [P, L, F, P],
-    "dk_conv_silu": [P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
+    "dk_conv_silu": [P, I, P, P, P, P, P, P, P, P, I, I, I, I, P, I, I, P],
     "dk_selective_scan": [P, P, P, I, I, I, P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P, P, P],
     "dk_attention_rows_plain": [C.POINTER(RowAttnParams), P],
     "dk_rows_append": [P, I, P, P, P, I, P, I, P, I, I, I, I, I, I, I, I, I, I, I, I, I, P, P],
@@ -91,7 +91,7 @@ _SIGNATURES = {
     "dk_embedding_pair": [P, P, P, P, P, P, P, F, P, L, L, L, P, P, I, I, I, I, P, P],
     "dk_remember_tokens": [P, P, P, P, P, I, P],
     "dk_residual_norm": [P, P, P, P, P, P, P, P, I, I, F, I, I, I, I, P],
-    "dk_rows_append_unit": [P, I, P, P, P, I, P, I, P, I, I, I, I, I, I, I, I, I, I, I, I, I, F, I, I, P, P],
+    "dk_rows_append_unit": [P, I, P, P, P, I, P, I, P, I, I, I, I, I, I, I, I, I, I, I, I, I, F, I, P, P, P, F, I, P, P],
     "dk_decay_attention_slice": [I, I, I, I],
     "dk_decay_attention": [P, I, I, I, I, I, P, P, P, P, P, P, I, I, I, I, I, I, P],
     "dk_decay_attention_chunk": [],
@@ -99,10 +99,16 @@ _SIGNATURES = {
     "dk_decay_attention_chunked": [P, I, I, I, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
     "dk_decay_attention_step_supported": [I, I],
     "dk_decay_attention_step": [P, I, I, I, I, I, P, P, P, P, P, I, I, I, I, I, P],
-    "dk_gated_rms_norm": [P, P, I, P, P, I, I, F, I, P],
+    "dk_normed_sum": [P, P, P, P, P, P, P, I, I, F, F, P],
+    "dk_add_bias": [P, P, I, I, I, P],
+    "dk_sigmoid_gate": [P, P, I, P, I, I, I, P],
+    "dk_gated_recurrence": [P, P, L, L, I, P, P, P, P, I, P, I, P, P, P, P, P, I, I, I, I, P, P, I, P],
+    "dk_matrix_memory_slice": [I, I, I, I],
+    "dk_matrix_memory": [P, I, I, I, I, F, P, P, F, F, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
+    "dk_gated_rms_norm": [P, P, I, P, P, I, I, F, I, I, P],
     "dk_glu_clamped": [P, P, L, I, F, F, F, I, P],
     "dk_router_topk": [P, I, P, P, I, I, I, P],
-    "dk_router": [P, P, P, P, P, I, I, I, I, I, I, P],
+    "dk_router": [P, P, P, P, P, I, I, I, I, I, P, F, I, I, P],
     "dk_experts_align": [P, I, I, P, I, P, I, I, P],
     "dk_experts_gather": [P, P, I, P, I, I, P],
     "dk_experts_gemm_tc_supported": [I, I, I],

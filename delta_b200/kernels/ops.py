@@ -469,10 +469,11 @@ def softcap(logits, cap: float):
 
 # ---- the selective state-space mixer ----------------------------------------------------------------------
 
-def conv_silu(xin, in_stride, weight, bias, conv_state, out, *, tok_row, row_slot, row_q_start, row_q_len):
+def conv_silu(xin, in_stride, weight, bias, conv_state, out, *, tok_row, row_slot, row_q_start, row_q_len, in_bias=None, silu=True):
     """Causal convolution over each row's tokens and silu; ``xin`` holds a token's C inputs at the start of rows of
     ``in_stride`` elements.  ``conv_state`` [slots, taps-1, C] (float32) supplies the inputs before the step's first
-    token and is left holding the last taps-1 inputs of every row."""
+    token and is left holding the last taps-1 inputs of every row.  ``in_bias`` (float32 [C]) is added to every input
+    as it is read (the zeros before a request's first token stay zeros); ``silu`` False: no activation."""
     T, C_ = out.shape
     taps = weight.shape[1]
     i32, f32 = torch.int32, torch.float32
@@ -480,7 +481,7 @@ def conv_silu(xin, in_stride, weight, bias, conv_state, out, *, tok_row, row_slo
         _ptr(xin, "xin", out.dtype), int(in_stride), _ptr(weight, "weight", f32), _ptr(bias, "bias", f32),
         _ptr(conv_state, "conv_state", f32), _ptr(out, "out"), _ptr(tok_row, "tok_row", i32), _ptr(row_slot, "row_slot", i32),
         _ptr(row_q_start, "row_q_start", i32), _ptr(row_q_len, "row_q_len", i32), T, row_slot.shape[0], C_, taps,
-        dtype_code(out.dtype), _stream()), "conv_silu", 2 if taps > 1 else 1)
+        _ptr(in_bias, "in_bias", f32), int(bool(silu)), dtype_code(out.dtype), _stream()), "conv_silu", 2 if taps > 1 else 1)
     return out
 
 
@@ -599,10 +600,13 @@ def attention_rows_mma(params: RowAttnParams, max_m: int, splits: int = 1, scrat
 
 
 def rows_append_unit(src, tok_pos, tok_row, block_table, cache, *, H, KV, dk, dv, ps, row_width, k_off, v_off, table=None,
-                     rot_dims=0, interleaved=True, unit_eps=None, value_from_key=False, err=None):
+                     rot_dims=0, interleaved=True, unit_eps=None, value_from_key=False, bias=None, q_norm=None, k_norm=None,
+                     pre_eps=0.0, err=None):
     """As ``rows_append``, one warp per head in 32 bit: after the rotation every query and key head is divided by its root
     mean square, sqrt(mean(x^2) + ``unit_eps``) (None: not), and rounded once.  ``value_from_key``: ``src`` holds no v;
-    the value is the key as it was projected, before rotation and norm."""
+    the value is the key as it was projected, before rotation and norm.  ``bias`` (float32, one entry per column of q, k
+    and v) is added as the heads are read; ``q_norm`` / ``k_norm`` (float32 [dk]): the RMS norm with this weight and
+    ``pre_eps`` on every query / key head before the rotation."""
     T = src.shape[0]
     if cache is not None and (tuple(cache.shape[1:]) != (KV, ps, row_width) or cache.dtype != src.dtype):
         raise KernelError(f"rows_append_unit: cache has shape {tuple(cache.shape)} / {cache.dtype}, expected [pages, {KV}, {ps}, {row_width}] of {src.dtype}")
@@ -614,7 +618,8 @@ def rows_append_unit(src, tok_pos, tok_row, block_table, cache, *, H, KV, dk, dv
         _ptr(block_table, "block_table", i32), block_table.shape[1] if block_table is not None else 0, _ptr(cache, "cache"),
         cache.shape[0] if cache is not None else 0, _ptr(table, "table", torch.float32), table.shape[0] if table is not None else 0,
         int(rot_dims), int(bool(interleaved)), T, H, KV, dk, dv, ps, row_width, k_off, v_off, int(unit_eps is not None),
-        float(unit_eps or 0.0), int(bool(value_from_key)), dtype_code(src.dtype), _ptr(err, "err", i32), _stream()), "rows_append_unit")
+        float(unit_eps or 0.0), int(bool(value_from_key)), _ptr(bias, "bias", torch.float32), _ptr(q_norm, "q_norm", torch.float32),
+        _ptr(k_norm, "k_norm", torch.float32), float(pre_eps), dtype_code(src.dtype), _ptr(err, "err", i32), _stream()), "rows_append_unit")
 
 
 # ---- a residual stream of one 32-bit copy whose sublayers run side by side ---------------------------------------
@@ -738,12 +743,99 @@ def decay_attention_chunked(src, q_off, k_off, v_off, decays, state, out, work, 
     return out
 
 
-def gated_rms_norm(o, gate_ptr, gate_stride, weight, out, eps):
+def gated_rms_norm(o, gate_ptr, gate_stride, weight, out, eps, group=None):
     """out = o / sqrt(mean(o^2) + eps) * weight * sigmoid(gate) per token; ``o`` float32 [T, n]; the gate's n values of a token
-    lie at ``gate_ptr`` + t * ``gate_stride`` elements of the type of ``out``."""
+    lie at ``gate_ptr`` + t * ``gate_stride`` elements of the type of ``out``.  ``group``: the mean is taken over every ``group``
+    consecutive entries (one head) instead of the whole row."""
     T, n = o.shape
     _l.check(_l.load().dk_gated_rms_norm(_ptr(o, "o", torch.float32), gate_ptr, int(gate_stride), _ptr(weight, "weight", torch.float32),
-                                         _ptr(out, "out"), T, n, float(eps), dtype_code(out.dtype), _stream()), "gated_rms_norm")
+                                         _ptr(out, "out"), T, n, float(eps), int(group or n), dtype_code(out.dtype), _stream()), "gated_rms_norm")
+    return out
+
+
+# ---- sublayers side by side, an output gate, and two recurrent mixers ------------------------------------------------
+
+def normed_sum(branches, out, eps, factor=1.0):
+    """out = ``factor`` * sum over ``branches`` [(y, bias or None, weight)] of rms_norm(y + bias) * weight; one or two
+    branches, everything float32, y [T, d]."""
+    if not 1 <= len(branches) <= 2:
+        raise KernelError("normed_sum takes one or two branches")
+    f32 = torch.float32
+    T, d = branches[0][0].shape
+    args = []
+    for y, b, w in list(branches) + [(None, None, None)] * (2 - len(branches)):
+        if y is not None and tuple(y.shape) != (T, d):
+            raise KernelError(f"normed_sum: a branch has shape {tuple(y.shape)}, another {(T, d)}")
+        args += [_ptr(y, "branch", f32), _ptr(b, "bias", f32), _ptr(w, "weight", f32)]
+    _l.check(_l.load().dk_normed_sum(*args, _ptr(out, "out", f32), T, d, float(eps), float(factor), _stream()), "normed_sum")
+    return out
+
+
+def add_bias(y, bias):
+    """y[t] += bias (float32 [n]) in place; y [T, n] float32 or bfloat16."""
+    T, n = y.shape
+    _l.check(_l.load().dk_add_bias(_ptr(y, "y"), _ptr(bias, "bias", torch.float32), T, n, dtype_code(y.dtype), _stream()), "add_bias")
+    return y
+
+
+def sigmoid_gate(a, gate_ptr, gate_stride, out):
+    """out = a * sigmoid(g) element by element; the gate's values of token t lie at ``gate_ptr`` + t * ``gate_stride``
+    elements of the type of ``a``."""
+    T, n = a.shape
+    _l.check(_l.load().dk_sigmoid_gate(_ptr(a, "a"), gate_ptr, int(gate_stride), _ptr(out, "out", a.dtype), T, n, dtype_code(a.dtype),
+                                       _stream()), "sigmoid_gate")
+    return out
+
+
+def gated_recurrence(u, gates, block_size, r_bias, i_bias, decay, y_ptr, y_stride, y_bias, state, out, *, row_slot, row_q_start, row_q_len,
+                     gelu=True, seg_len=0, segs=1, seg_state=None, seg_decay=None):
+    """The gated diagonal recurrence over each row's tokens, from and into ``state`` [slots, C] (float32):
+    a = exp(decay * sigmoid(gr + r_bias)), S <- a S + sqrt(1 - a^2) sigmoid(gi + i_bias) u, out = S * act(y + y_bias).
+    ``gates`` float32, [T, 2C] (per block of ``block_size`` channels the decay gate's products, then the input gate's) or
+    [blocks, T, 2 block_size]; ``y_ptr``
+    addresses the gate branch in rows of ``y_stride`` elements of the type of ``u``.  ``seg_len`` > 0: rows are cut into segments
+    that run in parallel (three kernels), ``seg_state`` / ``seg_decay`` float32 [rows * segs * C] are working memory."""
+    T, C_ = u.shape
+    f32, i32 = torch.float32, torch.int32
+    if tuple(gates.shape) == (T, 2 * C_):
+        g_tok, g_block = 2 * C_, 2 * block_size
+    elif tuple(gates.shape) == (C_ // block_size, T, 2 * block_size):
+        g_tok, g_block = 2 * block_size, T * 2 * block_size
+    else:
+        raise KernelError(f"gated_recurrence: gates of shape {tuple(gates.shape)} do not fit {T} tokens of {C_} channels")
+    if tuple(state.shape[1:]) != (C_,):
+        raise KernelError(f"gated_recurrence: the state has shape {tuple(state.shape)}, expected [slots, {C_}]")
+    _l.check(_l.load().dk_gated_recurrence(
+        _ptr(u, "u"), _ptr(gates, "gates", f32), g_tok, g_block, int(block_size), _ptr(r_bias, "r_bias", f32), _ptr(i_bias, "i_bias", f32),
+        _ptr(decay, "decay", f32), y_ptr, int(y_stride), _ptr(y_bias, "y_bias", f32), int(bool(gelu)), _ptr(state, "state", f32),
+        _ptr(out, "out", u.dtype), _ptr(row_slot, "row_slot", i32), _ptr(row_q_start, "row_q_start", i32), _ptr(row_q_len, "row_q_len", i32),
+        row_slot.shape[0], C_, int(seg_len), int(segs), _ptr(seg_state, "seg_state", f32), _ptr(seg_decay, "seg_decay", f32),
+        dtype_code(u.dtype), _stream()), "gated_recurrence", 3 if seg_len > 0 else 1)
+    return out
+
+
+def matrix_memory_slice(rows, H, dk, dv) -> int:
+    return int(_l.load().dk_matrix_memory_slice(int(rows), H, dk, dv))
+
+
+def matrix_memory(src, q_off, k_off, v_off, q_scale, gates, gate_bias, cap, guard, S, z, m, out, *, H, dk, dv, row_slot, row_q_start,
+                  row_q_len, slice_=None):
+    """The matrix memory with exponential gates over each row's tokens, from and into ``S`` [slots, H, dk, dv], ``z`` [slots, H, dk]
+    and ``m`` [slots, H] (float32).  ``src`` [T, stride] holds a token's q, k (H*dk each) and v (H*dv) at the given offsets;
+    ``gates`` float32 [T, 2H] the input gates' products, then the forget gates'; ``gate_bias`` [2H]; ``out`` float32 [T, H*dv]."""
+    rows = row_slot.shape[0]
+    T = src.shape[0]
+    f32, i32 = torch.float32, torch.int32
+    if tuple(S.shape[1:]) != (H, dk, dv) or tuple(z.shape[1:]) != (H, dk) or tuple(m.shape[1:]) != (H,):
+        raise KernelError(f"matrix_memory: states of shapes {tuple(S.shape)}, {tuple(z.shape)}, {tuple(m.shape)} do not fit H={H} dk={dk} dv={dv}")
+    if tuple(out.shape) != (T, H * dv) or tuple(gates.shape) != (T, 2 * H):
+        raise KernelError(f"matrix_memory: out {tuple(out.shape)} or gates {tuple(gates.shape)} do not fit {T} tokens")
+    dvs = slice_ or matrix_memory_slice(rows, H, dk, dv)
+    _l.check(_l.load().dk_matrix_memory(
+        _ptr(src, "src"), src.shape[1], int(q_off), int(k_off), int(v_off), float(q_scale), _ptr(gates, "gates", f32),
+        _ptr(gate_bias, "gate_bias", f32), float(cap), float(guard), _ptr(S, "S", f32), _ptr(z, "z", f32), _ptr(m, "m", f32),
+        _ptr(out, "out", f32), _ptr(row_slot, "row_slot", i32), _ptr(row_q_start, "row_q_start", i32), _ptr(row_q_len, "row_q_len", i32),
+        rows, H, dk, dv, dvs, dtype_code(src.dtype), _stream()), "matrix_memory")
     return out
 
 
@@ -765,13 +857,17 @@ def router_topk(logits, experts, top, choice, weight):
                                       _ptr(weight, "weight", torch.float32), T, int(experts), int(top), _stream()), "router_topk")
 
 
-def router(x, w, experts, top, logits, choice, weight):
+def router(x, w, experts, top, logits, choice, weight, scoring="softmax", correction=None, scale=1.0):
     """logits = x w^T in 32 bit ([T, rows of w]; the first ``experts`` rows are the experts'), and per token the ``top`` largest of
-    the experts' logits with the softmax over them."""
+    the experts' logits with the softmax over them.  ``scoring`` "sigmoid": scores s = sigmoid(logit); the ``top`` largest of
+    s + ``correction`` (float32 [experts] or None) are chosen; the weights are the chosen s divided by their sum, times ``scale``."""
     T, d = x.shape
+    if scoring not in ("softmax", "sigmoid"):
+        raise KernelError(f"router: unknown scoring '{scoring}'")
     _l.check(_l.load().dk_router(_ptr(x, "x"), _ptr(w, "w", x.dtype), _ptr(logits, "logits", torch.float32), _ptr(choice, "choice", torch.int32),
-                                 _ptr(weight, "weight", torch.float32), T, d, w.shape[0], int(experts), int(top), dtype_code(x.dtype),
-                                 _stream()), "router")
+                                 _ptr(weight, "weight", torch.float32), T, d, w.shape[0], int(experts), int(top),
+                                 _ptr(correction, "correction", torch.float32), float(scale), int(scoring == "sigmoid"),
+                                 dtype_code(x.dtype), _stream()), "router")
 
 
 def experts_tile_rows() -> int:
@@ -802,21 +898,27 @@ def experts_gemm_tc_supported(n, k, glu=False) -> bool:
 def experts_gemm_tc(rows, w, out, tile_expert, tile_rows, *, n, row_map=None, glu=False, limit=-1.0, alpha=1.702, shift=1.0, err=None):
     """The experts' products on the tcgen05 tensor cores: ``rows`` [tiles * tile_rows, k] (bfloat16, tiles of 128 or 256 rows of
     one expert each), ``w`` [E, n (2n with ``glu``: gate rows, then up rows), k]; ``out`` row r (or ``row_map[r]``; negative: not
-    stored) takes the n results of row r, after the gated activation when ``glu``."""
+    stored) takes the n results of row r, after the gated activation when ``glu``; ``glu`` "relu_squared": ``w`` [E, n, k] and
+    relu(result)^2."""
     E, k = w.shape[0], w.shape[2]
     _l.check(_l.load().dk_experts_gemm_tc(_ptr(rows, "rows", torch.bfloat16), _ptr(w, "w", torch.bfloat16), _ptr(out, "out"),
                                           _ptr(tile_expert, "tile_expert", torch.int32), _ptr(row_map, "row_map", torch.int32),
                                           rows.shape[0], int(tile_rows), int(n), int(k), int(E), out.stride(0), dtype_code(out.dtype),
-                                          int(bool(glu)), float(limit), float(alpha), float(shift), _ptr(err, "err", torch.int32),
-                                          _stream()), "experts_gemm_tc")
+                                          2 if glu == "relu_squared" else int(bool(glu)), float(limit), float(alpha), float(shift),
+                                          _ptr(err, "err", torch.int32), _stream()), "experts_gemm_tc")
     return out
 
 
 def experts_gemm(a, w, out, sorted_slots, tile_expert, *, top, n, k, act=False, limit=-1.0, alpha=1.702, shift=1.0):
-    """For every tile of rows its expert's product (see ``csrc/experts.cu``); ``w`` is [E, n (2n with ``act``), k]."""
+    """For every tile of rows its expert's product (see ``csrc/experts.cu``).  ``act`` False: ``a`` holds the rows in sorted order, the
+    result goes to the slots in 32 bit.  ``act`` True / "gated": rows gathered from the tokens, ``w`` [E, 2n, k] (gate rows, then up rows),
+    the gated activation.  ``act`` "relu_squared": rows gathered, ``w`` [E, n, k], relu(product)^2."""
+    code = {False: 0, True: 1, "gated": 1, "relu_squared": 2}.get(act)
+    if code is None:
+        raise KernelError(f"experts_gemm: unknown activation '{act}'")
     _l.check(_l.load().dk_experts_gemm(_ptr(a, "a"), _ptr(w, "w", a.dtype), _ptr(out, "out"), _ptr(sorted_slots, "sorted_slots", torch.int32),
                                        _ptr(tile_expert, "tile_expert", torch.int32), tile_expert.numel(), int(top), int(n), int(k),
-                                       int(bool(act)), float(limit), float(alpha), float(shift), dtype_code(a.dtype), _stream()), "experts_gemm")
+                                       code, float(limit), float(alpha), float(shift), dtype_code(a.dtype), _stream()), "experts_gemm")
 
 
 def experts_combine(z, weight, out, shared=None, gate_logit=None, gate_stride=0):

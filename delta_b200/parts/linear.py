@@ -229,7 +229,17 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, out_dtype=None) -> torch.Tenso
         r = torch.mm(x, w.t())
         ops.count_library()
         return r
+    if out_dtype == torch.float32 and T > SMALL_M:      # many rows into a 32-bit result: the library's product with a 32-bit output
+        ops.count_launch()
+        r = torch.mm(x, w.t(), out_dtype=torch.float32)
+        ops.count_library()
+        return r
     out = torch.empty((T, N), dtype=out_dtype, device=x.device)
     if T:
         ops.gemm_nt_plain(x, w, out)
     return out
+
+
+def linear_f32(ctx, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x W^T with the sums left in 32 bit (for results that join a 32-bit stream or a recurrence unrounded)."""
+    return linear(ctx, x, w, out_dtype=torch.float32)

@@ -10,8 +10,15 @@ vector.  ``reentry`` describes a span of layers that runs several times: before 
 output (x as ``start`` made it) is added, and before every pass t the row t of the tensor ``reentry["name"]``
 [passes, d].
 
+A re-entry may instead be a projection (``reentry["project"]`` names a matrix W [d, 2 d]): before EVERY pass, the first
+too, x <- W [x ; x0] with x0 the embedding output.  The matrix is cut into its two halves W = [A | B]: B x0 is the same for
+every pass and is computed once per step; a pass then computes A x and hands B x0 on as the pending 32-bit stream that the
+next norm adds, so the sum costs no kernel.
+
 ``parallel`` block: h = norm1(x); x <- x + (mixer(h) + feed_forward(h)); one norm, both sublayers read it; the
 feed-forward may be absent.
+
+``residual_pre_norm`` block: x <- x + mixer(norm1(x)); x <- x + feed_forward(norm2(x)); the second sublayer may be absent.
 """
 from __future__ import annotations
 
@@ -21,10 +28,12 @@ from typing import Optional
 import torch
 
 from ..kernels import ops
+from . import linear
 from .base import BLOCKS, STREAMS, Block, StateSpec, Stream, TensorSpec
 
 PREV_TOKEN = "stream.prev_token"
 KEPT = "residual.embedding_output"
+PROJECTED = "residual.projected_embedding"
 
 
 @dataclass
@@ -55,30 +64,38 @@ def read(ctx, x, pending: Optional[Pending], norm, rows=None, write_back=True):
 class ResidualStream(Stream):
     def __init__(self, width: int, scale: float = 1.0, pair: Optional[dict] = None, reentry: Optional[dict] = None):
         """``pair``: {name, buckets, mul_prev, mul_cur} of the hashed pair table [buckets + 1, d] (None: none).
-        ``reentry``: {name, passes, add_embedding} (None: no span runs more than once)."""
+        ``reentry``: {name, passes, add_embedding}, or {project, passes} (None: no span runs more than once)."""
         self.width, self.scale = int(width), float(scale)
         self.pair = dict(pair) if pair else None
         self.reentry = dict(reentry) if reentry else None
-        self.pair_table = self.pass_vectors = None
+        self.projects = bool(self.reentry and self.reentry.get("project"))
+        self.pair_table = self.pass_vectors = self.w_stream = self.w_embed = None
 
     def tensor_specs(self):
         specs = []
         if self.pair:
             specs.append(TensorSpec(self.pair["name"], (int(self.pair["buckets"]) + 1, self.width), kind="table"))
-        if self.reentry:
+        if self.projects:
+            specs.append(TensorSpec(self.reentry["project"], (self.width, 2 * self.width), init="eye2"))
+        elif self.reentry:
             specs.append(TensorSpec(self.reentry["name"], (int(self.reentry["passes"]), self.width), kind="vector", init="normal"))
         return specs
 
     def bind(self, tensors):
         if self.pair:
             self.pair_table = tensors[self.pair["name"]]
-        if self.reentry:
+        if self.projects:
+            w = tensors[self.reentry["project"]]
+            self.w_stream, self.w_embed = w[:, :self.width].contiguous(), w[:, self.width:].contiguous()
+        elif self.reentry:
             self.pass_vectors = tensors[self.reentry["name"]].float().contiguous()
 
     def state_specs(self):
         return {PREV_TOKEN: StateSpec((1,), torch.int32, -1)} if self.pair else {}
 
     def _keeps(self) -> bool:
+        if self.projects:
+            return True
         return bool(self.reentry and self.reentry.get("add_embedding", True) and int(self.reentry["passes"]) > 1)
 
     def start(self, ctx, table):
@@ -95,11 +112,26 @@ class ResidualStream(Stream):
         if self.pair:
             ops.remember_tokens(ctx.tokens, state, row_q_start=ctx.row_q_start, row_q_len=ctx.row_q_len, row_slot=ctx.row_slot)
         self._kept = keep
+        self._projected = None
         return x
+
+    def _enter_projected(self, ctx, x, pending):
+        """x <- A x + B x0: the settled stream goes through A here, B x0 (made once per step) is left pending."""
+        T = x.shape[0]
+        if self._projected is None:
+            e = torch.empty((T, self.width), dtype=ctx.dtype, device=x.device)
+            ops.residual_norm(self._kept, e, write_back=False)          # the embedding output in the compute type
+            self._projected = linear.linear_f32(ctx, e, self.w_embed)
+        h = torch.empty((T, self.width), dtype=ctx.dtype, device=x.device)
+        p = pending or Pending()
+        ops.residual_norm(x, h, updates=p.updates, extra=p.extra, vec=p.vec, write_back=False)   # the settled stream, rounded once
+        return linear.linear_f32(ctx, h, self.w_stream), Pending((), self._projected, None)
 
     def enter_pass(self, ctx, x, pending, number: int):
         if not self.reentry:
             raise ValueError("the stream was built without a re-entry and is told that a pass starts")
+        if self.projects:
+            return self._enter_projected(ctx, x, pending)
         p = pending or Pending()
         if p.extra is not None or p.vec is not None:      # two re-entries without a layer between them: settle the first
             ops.residual_norm(x, None, updates=p.updates, extra=p.extra, vec=p.vec)
@@ -126,3 +158,23 @@ class ParallelBlock(Block):
         if self.feed_forward is not None:
             ys = ys + (self.feed_forward.forward(ctx, h),)
         return x, Pending(ys)
+
+
+@BLOCKS.register("residual_pre_norm")
+class ResidualPreNormBlock(Block):
+    """The pre-norm arrangement on the 32-bit stream; a layer may have no feed-forward (then it has no second norm either)."""
+    roles = ("norm1", "mixer")
+    optional_roles = ("norm2", "feed_forward")
+
+    def __init__(self, parts):
+        super().__init__(parts)
+        if (self.norm2 is None) != (self.feed_forward is None):
+            raise ValueError("the second norm and the feed-forward come together or not at all")
+
+    def forward(self, ctx, x, pending, cache):
+        h = read(ctx, x, pending, self.norm1)
+        y = self.mixer.forward(ctx, h, cache)
+        if self.feed_forward is None:
+            return x, Pending((y,))
+        f = read(ctx, x, Pending((y,)), self.norm2)
+        return x, Pending((self.feed_forward.forward(ctx, f),))

@@ -8,11 +8,18 @@ converter; on the rows of an unconverted model folder the same function pairs
 (j, j + head_dim/2), which is the default here.  ``interleaved=True`` gives the
 reference's pairing.
 
+``scaling`` {factor, low, high, original} stretches long wavelengths (the Llama 3.1 rule): with wavelength
+l = 2 pi / f, a frequency f is kept where l < original / high, divided by ``factor`` where l > original / low, and
+between the two blended, (1 - s) f / factor + s f with s = (original / l - low) / (high - low).
+
 Cos and sin are tabulated once per (head_dim, theta, scale) in 64 bit and
 rounded to 32 bit, so the kernels do no trigonometry and the angles carry no
 32-bit rounding of a large position times a small frequency.
 """
 from __future__ import annotations
+
+import math
+from typing import Optional
 
 import torch
 
@@ -23,7 +30,8 @@ _TABLES: dict = {}
 
 @POSITION_ENCODINGS.register("rotary")
 class RotaryPositions(PositionEncoding):
-    def __init__(self, head_dim: int, theta: float, max_positions: int, interleaved: bool = False, scale: float = 1.0):
+    def __init__(self, head_dim: int, theta: float, max_positions: int, interleaved: bool = False, scale: float = 1.0,
+                 scaling: Optional[dict] = None):
         if head_dim % 2:
             raise ValueError(f"rotary positions need an even head size, got {head_dim}")
         self.head_dim = int(head_dim)
@@ -31,17 +39,33 @@ class RotaryPositions(PositionEncoding):
         self.max_positions = int(max_positions)
         self.interleaved = bool(interleaved)
         self.scale = float(scale)
+        self.scaling = None
+        if scaling:
+            self.scaling = tuple(float(scaling[k]) for k in ("factor", "low", "high", "original"))
+            if self.scaling[2] == self.scaling[1]:
+                raise ValueError("rotary scaling: 'high' and 'low' must differ")
 
-    def table_cpu(self) -> torch.Tensor:
-        """[max_positions, head_dim/2, 2] float32: cos and sin of every angle."""
+    def frequencies(self) -> torch.Tensor:
+        """[head_dim/2] float64: the angle a position advances every pair by."""
         half = self.head_dim // 2
         j = torch.arange(half, dtype=torch.float64)
         inv = 1.0 / (self.scale * self.theta ** (2.0 * j / self.head_dim))
+        if self.scaling is not None:
+            factor, low, high, original = self.scaling
+            wave = 2.0 * math.pi / inv
+            s = (original / wave - low) / (high - low)
+            blend = (1.0 - s) * inv / factor + s * inv
+            inv = torch.where(wave < original / high, inv, torch.where(wave > original / low, inv / factor, blend))
+        return inv
+
+    def table_cpu(self) -> torch.Tensor:
+        """[max_positions, head_dim/2, 2] float32: cos and sin of every angle."""
+        inv = self.frequencies()
         ang = torch.arange(self.max_positions, dtype=torch.float64)[:, None] * inv[None, :]
         return torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).to(torch.float32).contiguous()
 
     def table(self, device) -> torch.Tensor:
-        key = (self.head_dim, self.theta, self.scale, self.max_positions, str(device))
+        key = (self.head_dim, self.theta, self.scale, self.scaling, self.max_positions, str(device))
         if key not in _TABLES:
             _TABLES[key] = self.table_cpu().to(device)
         return _TABLES[key]

@@ -14,6 +14,12 @@ key-value head h // (H / kv_heads)), with the options
   * ``unit_norm_eps``: after the rotation every query and key head is divided by its root mean square,
     sqrt(mean(x^2) + eps), with no weight (None: not);
   * ``value_from_key``: there is no value projection; a token's value is its key as projected, before rotation and norm.
+  * ``bias``: the q, k, v and output projections have biases (``<name>.b``), added to the products in 32 bit;
+  * ``qk_norm_eps``: before the rotation every query and key head goes through an RMS norm with a weight of the head's size
+    (``q.norm`` / ``k.norm``, the same for every head): x / sqrt(mean(x^2) + eps) * w (None: not);
+  * ``gate``: the heads' outputs are multiplied by sigmoid(W_g h) (``g`` [heads * value_dim, width], the mixer's own input h)
+    before the output projection;
+  * ``wide_output``: the output projection's result is handed on in 32 bit.
 Scores and softmax weights are 32 bit in every kernel of the family.  ``run`` chooses the kernels for a batch.
 """
 from __future__ import annotations
@@ -93,7 +99,8 @@ class SinkAttention(Mixer):
     def __init__(self, prefix: str, width: int, heads: int, kv_heads: int, head_dim: int, value_dim: Optional[int] = None,
                  window: Optional[int] = None, sink: bool = False, scale: Optional[float] = None,
                  position: Optional[PartSpec] = None, rot_dims: Optional[int] = None, names: Optional[dict] = None,
-                 sink_logit: Optional[float] = None, unit_norm_eps: Optional[float] = None, value_from_key: bool = False):
+                 sink_logit: Optional[float] = None, unit_norm_eps: Optional[float] = None, value_from_key: bool = False,
+                 bias: bool = False, qk_norm_eps: Optional[float] = None, gate: bool = False, wide_output: bool = False):
         if heads % kv_heads:
             raise ValueError(f"{heads} heads are no multiple of {kv_heads} key-value heads")
         self.prefix, self.width = prefix, int(width)
@@ -104,6 +111,10 @@ class SinkAttention(Mixer):
         self.sink_logit = float(sink_logit) if sink_logit is not None else None
         self.unit_norm_eps = float(unit_norm_eps) if unit_norm_eps is not None else None
         self.value_from_key = bool(value_from_key)
+        self.has_bias, self.has_gate, self.wide_output = bool(bias), bool(gate), bool(wide_output)
+        self.qk_norm_eps = float(qk_norm_eps) if qk_norm_eps is not None else None
+        self.fold_out_bias = False      # set by a container that adds the output bias itself (``out_bias``) in a kernel of its own
+        self.in_bias = self.out_bias = self.q_norm = self.k_norm = None
         if self.has_sink and self.sink_logit is not None:
             raise ValueError("a learned sink and a fixed sink logit exclude one another")
         if self.value_from_key and self.dv != self.dk:
@@ -111,7 +122,7 @@ class SinkAttention(Mixer):
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.dk)
         self.position = position.build(POSITION_ENCODINGS) if position is not None else None
         self.rot_dims = int(rot_dims) if rot_dims else (self.dk if position is not None else 0)
-        self.names = dict(q="q", k="k", v="v", o="o", sink="sink")
+        self.names = dict(q="q", k="k", v="v", o="o", sink="sink", g="g")
         self.names.update(names or {})
         self.w_qkv = self.w_o = self.sink = None
 
@@ -123,12 +134,31 @@ class SinkAttention(Mixer):
         specs.append(TensorSpec(p + n["o"], (d, self.heads * self.dv)))
         if self.has_sink:
             specs.append(TensorSpec(p + n["sink"], (self.heads,), kind="vector", init="uniform:-1:1"))
+        if self.has_gate:
+            specs.append(TensorSpec(p + n["g"], (self.heads * self.dv, d)))
+        if self.has_bias:
+            specs += [TensorSpec(p + n["q"] + ".b", (self.heads * self.dk,), kind="vector", init="uniform:-0.1:0.1"),
+                      TensorSpec(p + n["k"] + ".b", (self.kv_heads * self.dk,), kind="vector", init="uniform:-0.1:0.1"),
+                      TensorSpec(p + n["o"] + ".b", (d,), kind="vector", init="uniform:-0.1:0.1")]
+            if not self.value_from_key:
+                specs.append(TensorSpec(p + n["v"] + ".b", (self.kv_heads * self.dv,), kind="vector", init="uniform:-0.1:0.1"))
+        if self.qk_norm_eps is not None:
+            specs += [TensorSpec(p + n["q"] + ".norm", (self.dk,), kind="vector", init="norm"),
+                      TensorSpec(p + n["k"] + ".norm", (self.dk,), kind="vector", init="norm")]
         return specs
 
     def bind(self, tensors):
         p, n = self.prefix, self.names
         mats = [tensors[p + n["q"]], tensors[p + n["k"]]] + ([] if self.value_from_key else [tensors[p + n["v"]]])
+        if self.has_gate:      # the gate's rows ride behind q, k and v in one product
+            mats.append(tensors[p + n["g"]])
         self.w_qkv = torch.cat(mats, dim=0).contiguous()
+        if self.has_bias:
+            parts = [tensors[p + n["q"] + ".b"], tensors[p + n["k"] + ".b"]] + ([] if self.value_from_key else [tensors[p + n["v"] + ".b"]])
+            self.in_bias = torch.cat([t.float() for t in parts]).contiguous()
+            self.out_bias = tensors[p + n["o"] + ".b"].float().contiguous()
+        if self.qk_norm_eps is not None:
+            self.q_norm, self.k_norm = tensors[p + n["q"] + ".norm"].float().contiguous(), tensors[p + n["k"] + ".norm"].float().contiguous()
         self.w_o = tensors[p + n["o"]]
         self.sink = tensors[p + n["sink"]].float().contiguous() if self.has_sink else None
         if self.sink_logit is not None:
@@ -145,13 +175,20 @@ class SinkAttention(Mixer):
         append = dict(H=H, KV=KV, dk=dk, dv=dv, ps=cache.page_size, row_width=dk + dv, k_off=0, v_off=dk, table=table,
                       rot_dims=self.rot_dims, interleaved=bool(getattr(self.position, "interleaved", True)), err=ctx.err)
         pages = cache.pages if cache.writes else None
-        if self.unit_norm_eps is not None or self.value_from_key:
+        if self.unit_norm_eps is not None or self.value_from_key or self.has_bias or self.qk_norm_eps is not None:
             ops.rows_append_unit(qkv, ctx.tok_pos, ctx.tok_row, cache.block_table, pages, unit_eps=self.unit_norm_eps,
-                                 value_from_key=self.value_from_key, **append)
+                                 value_from_key=self.value_from_key, bias=self.in_bias, q_norm=self.q_norm, k_norm=self.k_norm,
+                                 pre_eps=self.qk_norm_eps or 0.0, **append)
         else:
             ops.rows_append(qkv, ctx.tok_pos, ctx.tok_row, cache.block_table, pages, **append)
         out = torch.empty((x.shape[0], H * dv), dtype=x.dtype, device=x.device)
         params = make_params(ctx, q=qkv, q_stride=qkv.shape[1], q_head_stride=dk, out=out, cache=cache, H=H, KV=KV, dk=dk, dv=dv,
                              row_width=dk + dv, k_off=0, v_off=dk, scale=self.scale, window=self.window, sink=self.sink)
         run(ctx, params)
-        return linear.linear(ctx, out, self.w_o)
+        if self.has_gate:
+            g_at = qkv.data_ptr() + ((H + KV) * dk + (0 if self.value_from_key else KV * dv)) * qkv.element_size()
+            ops.sigmoid_gate(out, g_at, qkv.shape[1], out)
+        y = linear.linear(ctx, out, self.w_o, out_dtype=torch.float32 if self.wide_output else None)
+        if self.out_bias is not None and not self.fold_out_bias:
+            ops.add_bias(y, self.out_bias)
+        return y

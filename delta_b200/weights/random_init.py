@@ -27,6 +27,10 @@ def _draw(spec: TensorSpec, gen: torch.Generator, device) -> torch.Tensor:
         return 1.0 + (torch.rand(spec.shape, generator=gen, device=device, dtype=torch.float32) * 0.2 - 0.1)
     if spec.init == "zeros":
         return torch.zeros(spec.shape, device=device, dtype=torch.float32)
+    if spec.init == "eye2":       # [d, 2d]: half of each of two vectors stacked behind one another, plus noise
+        d = spec.shape[0]
+        eye = torch.eye(d, device=device, dtype=torch.float32)
+        return 0.5 * torch.cat([eye, eye], dim=1) + torch.randn(spec.shape, generator=gen, device=device, dtype=torch.float32) * 0.02
     if spec.init.startswith("uniform:"):      # "uniform:a:b": U(a, b)
         a, b = (float(v) for v in spec.init.split(":")[1:3])
         return a + (b - a) * torch.rand(spec.shape, generator=gen, device=device, dtype=torch.float32)
