@@ -419,13 +419,30 @@ def pibalorn_config(d: int) -> dict:
                         dict(att, mlp=experts)])
 
 
+def mufalix_config(d: int) -> dict:
+    """A Mufalix model with layers of the sizes of a real model of width d: a matrix-memory layer (d/128 heads of 128 x 128), then
+    a layer of two mixers side by side (attention of d/128 heads on d/512 key-value heads over a window of 1,024 tokens, 64 of 128
+    entries rotated with scaled frequencies; a recurrence of d channels in groups of 128 behind a convolution of 4 taps) and a
+    second matrix-memory layer that run twice, then another pair; every layer with a mixture of 16 experts (4 chosen, d/2 wide)."""
+    H = d // 128
+    mem = dict(type="mlstm", mixer=dict(heads=H, dim=128, vdim=128, gate_cap=15.0))
+    pair = dict(type="parallel", mixer=dict(
+        left=dict(heads=H, kv_heads=max(1, H // 4), dim=128, vdim=128, scale=0.09, mask=dict(size=1024),
+                  rot=dict(base=500000.0, dims=64, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192))),
+        right=dict(width=d, conv=4, blocks=H)))
+    experts = dict(kind="moe", router=dict(experts=16, top=4, scale=2.5), expert=dict(ff=d // 2))
+    return dict(architecture="Mufalix", vocab=32000, width=d, norm=dict(eps=1e-5), embedding=dict(scale=float(d) ** 0.5),
+                loop=dict(start=1, stop=3, times=2),
+                layers=[dict(mem, mlp=experts), dict(pair, mlp=experts), dict(mem, mlp=experts), dict(pair, mlp=experts)])
+
+
 def roletar_workload(args) -> int:
     return design_workload(args, "roletar")
 
 
 def design_workload(args, design: str) -> int:
-    """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 at context 2,048) of a design (Roletar, Pibalorn) beside the
-    Yi architecture at equal width and layer count, through ``ModelRunner.step``, timed with CUDA events after warm-up with
+    """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 at context 2,048) of a design (Roletar, Pibalorn, Mufalix) beside the
+    Yi architecture at equal width and layer count (Mufalix also beside Pibalorn, the closest design), through ``ModelRunner.step``, timed with CUDA events after warm-up with
     the L2 flushed before every timed step; then every launcher's share of one such step, with the fraction of the measured
     peaks that the design's own kernels and their Yi counterparts reach."""
     import torch
@@ -506,10 +523,13 @@ def design_workload(args, design: str) -> int:
 
     launches = 0
     for d in args.width:
-        rc = roletar_config(d) if design == "roletar" else pibalorn_config(d)
+        rc = {"roletar": roletar_config, "pibalorn": pibalorn_config, "mufalix": mufalix_config}[design](d)
         runs = 6
         yc = yi_like_config(d, runs)
         a, b = measure(rc, rc["vocab"]), measure(yc, yc["vocab_size"])
+        if design == "mufalix":     # the closest design of the engine (32-bit stream, a recurrent state, experts, a repeated span) as well
+            pc = pibalorn_config(d)
+            c = measure(pc, pc["vocab"])
         launches += a["launches_per_decode_step"]
         H = d // 128
         # what the kernels of one step have to move or compute, per launcher (prefill of T tokens unless said otherwise)
@@ -524,10 +544,10 @@ def design_workload(args, design: str) -> int:
             "gemm_nt_plain_batched": (0, 2 * T * H * (128 * 256 + 256 * 128) * 4),
             "attention_rows_mma": (0, 4 * (2 * H * (320 + 256) * T * (T + 1) // 2) + 2 * H * 256 * (1024 * T - 1024 * 1023 // 2)),
         }
-        if design == "pibalorn":
-            G, E, top, F = max(1, H // 4), 16, 4, d // 2
+        def pibalorn_work():
+            G, top, F = max(1, H // 4), 4, d // 2
             n_lin, n_att, n_moe = 3, 3, 5          # runs of a linear-attention layer, of an attention layer, of a mixture
-            work = {
+            return {
                 "residual_norm": ((2 * d * 4 + 3 * d * 2) * T * runs, 0),
                 "embedding_pair": ((2 * d * 2 + 2 * d * 4) * T, 0),
                 "glu_clamped": (3 * (((8 * d // 3 + 255) // 256 * 256) + n_moe * F) * 2 * T, 0),
@@ -537,6 +557,25 @@ def design_workload(args, design: str) -> int:
                 "decay_attention": (0, 2 * T * H * (2 * 128 * 128 + 16 * (128 + 128)) * n_lin),
                 "experts_gemm": (0, 2 * T * top * 3 * d * F * n_moe),
                 "attention_rows_mma": (0, 4 * 128 * H * (T * (T + 1) // 2) * n_att),
+            }
+        if design == "pibalorn":
+            work = pibalorn_work()
+        if design == "mufalix":
+            G, top, F, Wn = max(1, H // 4), 4, d // 2, 1024
+            n_mem, n_pair, n_moe = 3, 3, 6          # runs of a matrix-memory layer, of a pair of mixers, of a mixture
+            seen = Wn * T - Wn * (Wn - 1) // 2       # (query, key) pairs inside the window
+            work = {
+                "residual_norm": ((2 * d * 4 + 2 * d * 4 + d * 2) * T * (2 * runs), 0),
+                "matrix_memory": (0, 2 * T * H * (2 * 128 * 128 + 16 * (128 + 128)) * n_mem),     # counted as the linear attention's
+                "gated_rms_norm": ((H * 128 * 4 + 2 * H * 128 * 2) * T * (n_mem + n_pair), 0),
+                "gated_recurrence": ((2 * d * 4 + 3 * d * 2) * T * n_pair, 0),
+                "conv_silu": (2 * d * 2 * T * n_pair, 0),
+                "normed_sum": (3 * d * 4 * T * n_pair, 0),
+                "rows_append": ((2 * H + 4 * G) * 128 * 2 * T * n_pair, 0),
+                "activation": (2 * top * F * 2 * T * n_moe, 0),
+                "experts_combine": ((top * d * 4 + d * 4) * T * n_moe, 0),
+                "experts_gemm": (0, 2 * T * top * 2 * d * F * n_moe),
+                "attention_rows_mma": (0, 4 * 128 * H * seen * n_pair),
             }
         yi_work = {
             "rms_norm": (4 * d * 2 * T * (2 * runs) , 0),
@@ -568,6 +607,11 @@ def design_workload(args, design: str) -> int:
                    "decode_ms": b["decode_ms"], "decode_graph_ms": b["decode_graph_ms"], "launches_per_decode_step": b["launches_per_decode_step"],
                    "prefill_launchers": fractions(b["prefill_launchers"], yi_work),
                    "decode_launchers": fractions(b["decode_launchers"], {})},
+            **({"pibalorn": {"prefill_tok_s": T / c["prefill_ms"] * 1e3, "prefill_ms": c["prefill_ms"], "decode_tok_s": B / c["decode_ms"] * 1e3,
+                             "decode_ms": c["decode_ms"], "decode_graph_ms": c["decode_graph_ms"],
+                             "launches_per_decode_step": c["launches_per_decode_step"],
+                             "prefill_launchers": fractions(c["prefill_launchers"], pibalorn_work()),
+                             "decode_launchers": fractions(c["decode_launchers"], {})}} if design == "mufalix" else {}),
             "config": {"width": d, "layer_runs": runs, "prefill_tokens": T, "decode_batch": B, "decode_context": CTX,
                        "l2": "flushed before every timed step"}}
     first = out["sizes"][str(args.width[0])]
@@ -593,8 +637,8 @@ def main() -> int:
     ap.add_argument("--enable_selective_cache", action="store_true", help="DELTA on (not the default run)")
     ap.add_argument("--full_cache_layers", nargs="+", type=int, default=[0, 1, 2, 14, 22])
     ap.add_argument("--subset_cache_size", type=int, default=64)
-    ap.add_argument("--workload", choices=["decode", "baseline", "yi9b-long", "yi34b-mixed", "grown", "long-prompt", "roletar", "pibalorn"], default="decode")
-    ap.add_argument("--width", type=int, nargs="+", default=[2048, 4096], help="--workload roletar / pibalorn: the model widths that are measured")
+    ap.add_argument("--workload", choices=["decode", "baseline", "yi9b-long", "yi34b-mixed", "grown", "long-prompt", "roletar", "pibalorn", "mufalix"], default="decode")
+    ap.add_argument("--width", type=int, nargs="+", default=[2048, 4096], help="--workload roletar / pibalorn / mufalix: the model widths that are measured")
     ap.add_argument("--generate", type=int, default=None, help="tokens generated per request in the other workloads (default: what the workload names)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -604,7 +648,7 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
-    if args.workload in ("roletar", "pibalorn"):
+    if args.workload in ("roletar", "pibalorn", "mufalix"):
         return design_workload(args, args.workload)
     if args.workload != "decode":
         return other_workload(args)

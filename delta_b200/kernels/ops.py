@@ -839,6 +839,43 @@ def matrix_memory(src, q_off, k_off, v_off, q_scale, gates, gate_bias, cap, guar
     return out
 
 
+def matrix_memory_chunk() -> int:
+    """Tokens of a chunk on the path that runs a row's chunks in parallel."""
+    return int(_l.load().dk_matrix_memory_chunk())
+
+
+def matrix_memory_chunked_supported(dk, dv) -> bool:
+    return bool(_l.load().dk_matrix_memory_chunked_supported(int(dk), int(dv)))
+
+
+def matrix_memory_chunked_work(total_chunks, H, dk, dv) -> int:
+    """Floats of work space for that many chunks: every chunk's memory, keys' sum and four numbers."""
+    return int(total_chunks) * H * (dk * dv + dk + 4)
+
+
+def matrix_memory_chunked(src, q_off, k_off, v_off, q_scale, gates, gate_bias, cap, guard, S, z, m, out, work, chunk_base, total_chunks,
+                          max_chunks, *, H, dk, dv, row_slot, row_q_start, row_q_len):
+    """``matrix_memory`` for long portions: every row is cut into chunks that run in parallel (three kernels: every chunk alone from
+    an empty memory, the memories and maxima before the chunks in order, every chunk's outputs).  ``chunk_base`` [rows] int32: the
+    chunks of all rows before each row; ``work`` float32 of ``matrix_memory_chunked_work(total_chunks, ...)`` entries."""
+    rows = row_slot.shape[0]
+    T = src.shape[0]
+    f32, i32 = torch.float32, torch.int32
+    if tuple(S.shape[1:]) != (H, dk, dv) or tuple(z.shape[1:]) != (H, dk) or tuple(m.shape[1:]) != (H,):
+        raise KernelError(f"matrix_memory_chunked: states of shapes {tuple(S.shape)}, {tuple(z.shape)}, {tuple(m.shape)} do not fit H={H} dk={dk} dv={dv}")
+    if tuple(out.shape) != (T, H * dv) or tuple(gates.shape) != (T, 2 * H):
+        raise KernelError(f"matrix_memory_chunked: out {tuple(out.shape)} or gates {tuple(gates.shape)} do not fit {T} tokens")
+    if work.numel() < matrix_memory_chunked_work(total_chunks, H, dk, dv):
+        raise KernelError(f"matrix_memory_chunked: {work.numel()} floats of work space are too few for {total_chunks} chunks")
+    _l.check(_l.load().dk_matrix_memory_chunked(
+        _ptr(src, "src"), src.shape[1], int(q_off), int(k_off), int(v_off), float(q_scale), _ptr(gates, "gates", f32),
+        _ptr(gate_bias, "gate_bias", f32), float(cap), float(guard), _ptr(S, "S", f32), _ptr(z, "z", f32), _ptr(m, "m", f32),
+        _ptr(out, "out", f32), _ptr(work, "work", f32), _ptr(row_slot, "row_slot", i32), _ptr(row_q_start, "row_q_start", i32),
+        _ptr(row_q_len, "row_q_len", i32), _ptr(chunk_base, "chunk_base", i32), rows, int(total_chunks), int(max_chunks), H, dk, dv,
+        dtype_code(src.dtype), _stream()), "matrix_memory_chunked", 3)
+    return out
+
+
 # ---- gated feed-forwards and a mixture of experts ---------------------------------------------------------------
 
 def glu_clamped(gate_up, out, limit=-1.0, alpha=1.702, shift=1.0):

@@ -20,7 +20,7 @@ from ..kernels import ops
 from . import linear
 from .base import MIXERS, Mixer, StateSpec, TensorSpec
 
-SEGMENT = 64            # tokens of a segment when a long portion's recurrence runs in parallel pieces
+SEGMENT = 16            # tokens of a segment when a long portion's recurrence runs in parallel pieces
 CONV_STATE = "conv"
 SCAN_STATE = "recurrence"
 

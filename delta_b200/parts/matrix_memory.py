@@ -8,7 +8,9 @@ With mixer input h, H heads, key size dk and value size dv:
     out = W_o ( o / rms(o per head) * w * sigmoid(W_g h) )
 S [H, dk, dv], z [H, dk] and m [H] start at zero (m too: not at minus infinity), live in 32 bit, one set per run of the layer,
 and are carried from step to step, so a prompt may be cut anywhere.  q, k, v and the output gate are one product; the two
-gates' rows are a second, small product whose sums stay 32 bit.
+gates' rows are a second, small product whose sums stay 32 bit.  Steps of short portions and single tokens take the tokens in
+turn, one block per (row, head, slice of the value entries); long portions run their chunks of 32 tokens in parallel
+(``csrc/matrix_memory_chunked.cu``).
 """
 from __future__ import annotations
 
@@ -18,6 +20,7 @@ from ..kernels import ops
 from . import linear
 from .base import MIXERS, Mixer, StateSpec, TensorSpec
 
+PARALLEL_FROM = 65      # portions of at least this many tokens run their chunks in parallel
 MEMORY = "memory"
 NORMALIZER = "normalizer"
 MAXIMUM = "maximum"
@@ -65,9 +68,24 @@ class MatrixMemory(Mixer):
         gates = linear.linear_f32(ctx, x, self.w_gates)               # [T, 2H], before bias, cap and logsigmoid
         o = torch.empty((T, H * dv), dtype=torch.float32, device=x.device)
         st = cache.state
-        ops.matrix_memory(qkvg, 0, H * dk, 2 * H * dk, dk ** -0.5, gates, self.gate_bias, self.cap, self.guard, st[MEMORY],
-                          st[NORMALIZER], st[MAXIMUM], o, H=H, dk=dk, dv=dv, row_slot=ctx.row_slot, row_q_start=ctx.row_q_start,
-                          row_q_len=ctx.row_q_len)
+        rows = dict(row_slot=ctx.row_slot, row_q_start=ctx.row_q_start, row_q_len=ctx.row_q_len)
+        if not ctx.replayable and ctx.max_q_len >= PARALLEL_FROM and ops.matrix_memory_chunked_supported(dk, dv):
+            # long portions: once the running maxima are known the recurrence is linear in the memory, so a row's chunks run in
+            # parallel and are stitched together in order
+            chunk = ops.matrix_memory_chunk()
+
+            def layout():
+                counts = [-(-n // chunk) for n in ctx.host["q_lens"]]
+                base = [sum(counts[:i]) for i in range(len(counts))]
+                return torch.tensor(base, dtype=torch.int32).to(x.device, non_blocking=True), sum(counts), max(counts)
+            base, total, most = ctx.memo(("matrix_memory chunks", chunk), layout)
+            bound = ops.matrix_memory_chunked_work(-(-ctx.max_step_tokens // chunk) + ctx.max_rows, H, dk, dv)
+            work = ctx.scratch("matrix_memory.chunks", (ops.matrix_memory_chunked_work(total, H, dk, dv),), torch.float32, bound=(bound,))
+            ops.matrix_memory_chunked(qkvg, 0, H * dk, 2 * H * dk, dk ** -0.5, gates, self.gate_bias, self.cap, self.guard, st[MEMORY],
+                                      st[NORMALIZER], st[MAXIMUM], o, work, base, total, most, H=H, dk=dk, dv=dv, **rows)
+        else:
+            ops.matrix_memory(qkvg, 0, H * dk, 2 * H * dk, dk ** -0.5, gates, self.gate_bias, self.cap, self.guard, st[MEMORY],
+                              st[NORMALIZER], st[MAXIMUM], o, H=H, dk=dk, dv=dv, **rows)
         y = torch.empty((T, H * dv), dtype=x.dtype, device=x.device)
         g_at = qkvg.data_ptr() + (2 * H * dk + H * dv) * qkvg.element_size()
         ops.gated_rms_norm(o, g_at, qkvg.shape[1], self.norm_w, y, self.eps, group=dv)

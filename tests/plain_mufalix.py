@@ -190,13 +190,14 @@ def capped(z, cap):
     return cap * torch.tanh(z / cap)
 
 
-def matrix_memory(q, k, v, log_i, log_f):
+def matrix_memory(q, k, v, log_i, log_f, with_condition=False):
     """q, k [T, H, n], v [T, H, m], log gates [T, H] -> [T, H, m].  Per head, with a running maximum mx that starts at 0:
     mx' = max(log_f + mx, log_i);  S' = exp(log_f + mx - mx') S + exp(log_i - mx') k v^T;  z likewise from k alone;
     out = S'^T q / (max(|z' . q|, exp(-mx')) + 1e-6)."""
     T, H, n = q.shape
     m = v.shape[-1]
     out = torch.zeros(T, H, m, dtype=F)
+    cond = torch.zeros(T, H, dtype=F)
     for h in range(H):
         S = torch.zeros(n, m, dtype=F)
         z = torch.zeros(n, dtype=F)
@@ -209,7 +210,8 @@ def matrix_memory(q, k, v, log_i, log_f):
             mx = new
             den = torch.maximum((z @ q[t, h]).abs(), torch.exp(-mx)) + 1e-6
             out[t, h] = (S.T @ q[t, h]) / den
-    return out
+            cond[t, h] = (z * q[t, h]).abs().sum() / den
+    return (out, cond) if with_condition else out
 
 
 def matrix_memory_mixer(cfg_m, W, p, h, eps):
@@ -227,12 +229,20 @@ def matrix_memory_mixer(cfg_m, W, p, h, eps):
 
 # ---------------------------------------------------------------- the experts
 
+MARGINS = None      # a list: every call of ``route`` appends its tokens' margins [T] here and their choices [T, top] to CHOICES
+CHOICES = []
+
+
 def route(h, w_router, correction, top, scale):
     """Sigmoid scores; the ``top`` largest of score + correction are chosen (lowest index among equals); their weights are
     the scores without the correction, divided by their sum, times ``scale``.  Returns (choice [T, top], weight [T, top])."""
     s = torch.sigmoid(h @ w_router.to(F).T)
     pick = s + correction.to(F)
-    order = torch.sort(pick, dim=-1, descending=True, stable=True).indices[:, :top]
+    ranked = torch.sort(pick, dim=-1, descending=True, stable=True)
+    order = ranked.indices[:, :top]
+    if MARGINS is not None:      # how far the last chosen expert is ahead of the first one left out, and the choice as a set
+        MARGINS.append(ranked.values[:, top - 1] - ranked.values[:, top] if top < pick.shape[-1] else torch.full_like(pick[:, 0], 9.0))
+        CHOICES.append(torch.sort(order, dim=-1).values)
     w = torch.gather(s, 1, order)
     return order, w / (w.sum(-1, keepdim=True) + 1e-20) * scale
 
