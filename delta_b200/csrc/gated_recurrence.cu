@@ -95,7 +95,7 @@ __global__ void matrix_memory_kernel(const T* __restrict__ src, int src_stride, 
                                      const float* __restrict__ gates, const float* __restrict__ gate_bias, float cap, float guard,
                                      float* __restrict__ S_state, float* __restrict__ z_state, float* __restrict__ m_state,
                                      float* __restrict__ out, const int* __restrict__ row_slot, const int* __restrict__ row_q_start,
-                                     const int* __restrict__ row_q_len, int H, int dk, int dv, int dvs) {
+                                     const int* __restrict__ row_q_len, int H, int dk, int dv, int dvs, int keep_zm) {
   extern __shared__ float sm[];
   float* S = sm;                    // [dk][dvs]
   float* z = S + (size_t)dk * dvs;  // [dk]
@@ -143,9 +143,110 @@ __global__ void matrix_memory_kernel(const T* __restrict__ src, int src_stride, 
   __syncthreads();
   for (int i = 0; i < dk; ++i)
     if (live) Sg[(size_t)i * dv + j0 + j] = S[(size_t)i * dvs + j];
-  if (blockIdx.z == 0) {
+  if (keep_zm) {      // (with several slices every block still reads them: matrix_memory_sums_kernel stores them afterwards)
     for (int i = threadIdx.x; i < dk; i += blockDim.x) zg[i] = z[i];
     if (threadIdx.x == 0) m_state[(size_t)slot * H + h] = m;
+  }
+}
+
+// The keys' sum z and the maximum m over a row's tokens, one block per (row, head): what matrix_memory_kernel leaves to a launch
+// of its own when a head's value entries are spread over several blocks, all of which read z and m as the step found them.
+template <typename T>
+__global__ void matrix_memory_sums_kernel(const T* __restrict__ src, int src_stride, int k_off, const float* __restrict__ gates,
+                                          const float* __restrict__ gate_bias, float cap, float* __restrict__ z_state,
+                                          float* __restrict__ m_state, const int* __restrict__ row_slot, const int* __restrict__ row_q_start,
+                                          const int* __restrict__ row_q_len, int H, int dk) {
+  const int row = blockIdx.x, h = blockIdx.y;
+  const int slot = row_slot[row], q0 = row_q_start[row], len = row_q_len[row];
+  float* zg = z_state + ((size_t)slot * H + h) * dk;
+  float m = m_state[(size_t)slot * H + h];
+  __syncthreads();
+  for (int t = 0; t < len; ++t) {
+    const size_t tok = (size_t)(q0 + t);
+    const float gi = gates[tok * 2 * H + h] + gate_bias[h], gf = gates[tok * 2 * H + H + h] + gate_bias[H + h];
+    const float li = cap * tanhf(gi / cap), lf = log_sigmoid_f(cap * tanhf(gf / cap));
+    const float m_new = fmaxf(lf + m, li);
+    const float keep = expf(lf + m - m_new), take = expf(li - m_new);
+    m = m_new;
+    for (int i = threadIdx.x; i < dk; i += blockDim.x)
+      zg[i] = fmaf(keep, zg[i], take * to_f32<T>(src[tok * src_stride + k_off + h * dk + i]));
+  }
+  if (threadIdx.x == 0) m_state[(size_t)slot * H + h] = m;
+}
+
+// ---- single tokens (decode steps): the memory streams through registers once ---------------------------------------------
+// One block per (row, head): 8 groups of 32 lanes; a lane owns four neighbouring value entries (16-byte accesses), group g the key
+// entries g, g + 8, ...; value entries beyond 128 are taken in turn.  S <- keep S + take k v^T is written back in place, o = S^T q
+// is summed over the groups in shared memory and divided by the denominator, which every thread has from a sum over the block.
+// The value size is a multiple of 4.
+template <typename T>
+__global__ void __launch_bounds__(256)
+matrix_memory_step_kernel(const T* __restrict__ src, int src_stride, int q_off, int k_off, int v_off, float q_scale,
+                          const float* __restrict__ gates, const float* __restrict__ gate_bias, float cap, float guard,
+                          float* __restrict__ S_state, float* __restrict__ z_state, float* __restrict__ m_state, float* __restrict__ out,
+                          const int* __restrict__ row_slot, const int* __restrict__ row_q_start, int H, int dk, int dv) {
+  extern __shared__ __align__(16) float sm[];
+  float4* red = reinterpret_cast<float4*>(sm);       // [8][32]
+  float* scratch = sm + 8 * 32 * 4;                  // [36]
+  float* q = scratch + 36;                           // [dk], scaled
+  float* k = q + dk;                                 // [dk], times the input gate's weight
+  const int row = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, grp = tid >> 5;
+  const size_t t = (size_t)row_q_start[row], slot = (size_t)row_slot[row] * H + h;
+  const T* tok = src + t * src_stride;
+  const float gi = gates[t * 2 * H + h] + gate_bias[h], gf = gates[t * 2 * H + H + h] + gate_bias[H + h];
+  const float li = cap * tanhf(gi / cap), lf = log_sigmoid_f(cap * tanhf(gf / cap));
+  const float m_old = m_state[slot];
+  const float m_new = fmaxf(lf + m_old, li);
+  const float keep = expf(lf + m_old - m_new), take = expf(li - m_new);
+  float* zg = z_state + slot * dk;
+  float zq = 0.f;
+  for (int i = tid; i < dk; i += 256) {
+    const float qv = to_f32<T>(tok[q_off + (size_t)h * dk + i]) * q_scale, kv = take * to_f32<T>(tok[k_off + (size_t)h * dk + i]);
+    const float zn = fmaf(keep, zg[i], kv);
+    q[i] = qv;
+    k[i] = kv;
+    zg[i] = zn;
+    zq = fmaf(zn, qv, zq);
+  }
+  zq = block_sum(zq, scratch);      // (its barriers also stand between every thread's read of m and the write below)
+  const float den = fmaxf(fabsf(zq), expf(-m_new)) + guard;
+  if (tid == 0) m_state[slot] = m_new;
+  float* Sg = S_state + slot * dk * dv;
+  for (int j0 = 0; j0 < dv; j0 += 128) {
+    const int j = j0 + lane * 4;
+    const bool live = j < dv;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f), o = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live) {
+      const T* vp = tok + v_off + (size_t)h * dv + j;
+      v = make_float4(to_f32<T>(vp[0]), to_f32<T>(vp[1]), to_f32<T>(vp[2]), to_f32<T>(vp[3]));
+      float* st = Sg + j;
+#pragma unroll 4
+      for (int i = grp; i < dk; i += 8) {
+        float4 s4 = *reinterpret_cast<const float4*>(st + (size_t)i * dv);
+        const float ki = k[i], qi = q[i];
+        s4.x = fmaf(keep, s4.x, ki * v.x);
+        s4.y = fmaf(keep, s4.y, ki * v.y);
+        s4.z = fmaf(keep, s4.z, ki * v.z);
+        s4.w = fmaf(keep, s4.w, ki * v.w);
+        *reinterpret_cast<float4*>(st + (size_t)i * dv) = s4;
+        o.x = fmaf(qi, s4.x, o.x);
+        o.y = fmaf(qi, s4.y, o.y);
+        o.z = fmaf(qi, s4.z, o.z);
+        o.w = fmaf(qi, s4.w, o.w);
+      }
+    }
+    red[grp * 32 + lane] = o;
+    __syncthreads();
+    if (grp == 0 && live) {
+      float4 a = red[lane];
+#pragma unroll
+      for (int g = 1; g < 8; ++g) {
+        const float4 b = red[g * 32 + lane];
+        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+      }
+      *reinterpret_cast<float4*>(out + t * ((size_t)H * dv) + (size_t)h * dv + j) = make_float4(a.x / den, a.y / den, a.z / den, a.w / den);
+    }
+    __syncthreads();
   }
 }
 
@@ -223,11 +324,39 @@ extern "C" int dk_matrix_memory(const void* src, int src_stride, int q_off, int 
     }                                                                                                                              \
     matrix_memory_kernel<T><<<grid, threads, smem, stream>>>((const T*)src, src_stride, q_off, k_off, v_off, q_scale, gates, gate_bias, \
                                                              cap, guard, S_state, z_state, m_state, out, row_slot, row_q_start,   \
-                                                             row_q_len, H, dk, dv, dvs);                                          \
+                                                             row_q_len, H, dk, dv, dvs, grid.z == 1);                             \
+    if (grid.z > 1)                                                                                                                \
+      matrix_memory_sums_kernel<T><<<dim3(rows, H), 128, 0, stream>>>((const T*)src, src_stride, k_off, gates, gate_bias, cap, z_state, \
+                                                                       m_state, row_slot, row_q_start, row_q_len, H, dk);         \
   } while (0)
   if (dtype == DK_F32) LAUNCH(float);
   else if (dtype == DK_BF16) LAUNCH(__nv_bfloat16);
   else DK_REQUIRE(false, "matrix_memory: unknown dtype %d", dtype);
 #undef LAUNCH
   return dk_check_launch("matrix_memory");
+}
+
+// Decode steps: every row brings one token.  The value size is a multiple of 4 and the memory and the output are 16-byte aligned.
+extern "C" int dk_matrix_memory_step_supported(int dk, int dv) { return dv % 4 == 0 && (size_t)(2 * dk + 36) * 4 + 8 * 32 * 16 <= 48 * 1024; }
+
+extern "C" int dk_matrix_memory_step(const void* src, int src_stride, int q_off, int k_off, int v_off, float q_scale, const float* gates,
+                                     const float* gate_bias, float cap, float guard, float* S_state, float* z_state, float* m_state,
+                                     float* out, const int* row_slot, const int* row_q_start, int rows, int H, int dk, int dv, int dtype,
+                                     cudaStream_t stream) {
+  if (rows == 0) return 0;
+  DK_REQUIRE(rows > 0 && H > 0 && dk > 0 && dv > 0, "matrix_memory_step: bad sizes rows=%d H=%d dk=%d dv=%d", rows, H, dk, dv);
+  DK_REQUIRE(cap > 0.f, "matrix_memory_step: the gates' cap must be positive");
+  DK_REQUIRE(dk_matrix_memory_step_supported(dk, dv) && ((uintptr_t)S_state % 16) == 0 && ((uintptr_t)out % 16) == 0,
+             "matrix_memory_step: heads of %d x %d are not taken (the value size must be a multiple of 4)", dk, dv);
+  DK_REQUIRE(H <= 65535, "matrix_memory_step: %d heads are above the grid's limit", H);
+  const dim3 grid(rows, H);
+  const size_t smem = (size_t)(2 * dk + 36) * sizeof(float) + 8 * 32 * sizeof(float4);
+#define LAUNCH(T)                                                                                                                      \
+  matrix_memory_step_kernel<T><<<grid, 256, smem, stream>>>((const T*)src, src_stride, q_off, k_off, v_off, q_scale, gates, gate_bias, cap, \
+                                                            guard, S_state, z_state, m_state, out, row_slot, row_q_start, H, dk, dv)
+  if (dtype == DK_F32) LAUNCH(float);
+  else if (dtype == DK_BF16) LAUNCH(__nv_bfloat16);
+  else DK_REQUIRE(false, "matrix_memory_step: unknown dtype %d", dtype);
+#undef LAUNCH
+  return dk_check_launch("matrix_memory_step");
 }

@@ -105,6 +105,8 @@ _SIGNATURES = {
     "dk_gated_recurrence": [P, P, L, L, I, P, P, P, P, I, P, I, P, P, P, P, P, I, I, I, I, P, P, I, P],
     "dk_matrix_memory_slice": [I, I, I, I],
     "dk_matrix_memory": [P, I, I, I, I, F, P, P, F, F, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
+    "dk_matrix_memory_step_supported": [I, I],
+    "dk_matrix_memory_step": [P, I, I, I, I, F, P, P, F, F, P, P, P, P, P, P, I, I, I, I, I, P],
     "dk_matrix_memory_chunk": [],
     "dk_matrix_memory_chunked_supported": [I, I],
     "dk_matrix_memory_chunked": [P, I, I, I, I, F, P, P, F, F, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],

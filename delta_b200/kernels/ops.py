@@ -839,6 +839,28 @@ def matrix_memory(src, q_off, k_off, v_off, q_scale, gates, gate_bias, cap, guar
     return out
 
 
+def matrix_memory_step_supported(dk, dv) -> bool:
+    return bool(_l.load().dk_matrix_memory_step_supported(int(dk), int(dv)))
+
+
+def matrix_memory_step(src, q_off, k_off, v_off, q_scale, gates, gate_bias, cap, guard, S, z, m, out, *, H, dk, dv, row_slot, row_q_start):
+    """``matrix_memory`` for steps in which every row brings one token: one block per (row, head) streams the memory through
+    registers once.  The value size is a multiple of 4."""
+    rows = row_slot.shape[0]
+    T = src.shape[0]
+    f32, i32 = torch.float32, torch.int32
+    if tuple(S.shape[1:]) != (H, dk, dv) or tuple(z.shape[1:]) != (H, dk) or tuple(m.shape[1:]) != (H,):
+        raise KernelError(f"matrix_memory_step: states of shapes {tuple(S.shape)}, {tuple(z.shape)}, {tuple(m.shape)} do not fit H={H} dk={dk} dv={dv}")
+    if tuple(out.shape) != (T, H * dv) or tuple(gates.shape) != (T, 2 * H):
+        raise KernelError(f"matrix_memory_step: out {tuple(out.shape)} or gates {tuple(gates.shape)} do not fit {T} tokens")
+    _l.check(_l.load().dk_matrix_memory_step(
+        _ptr(src, "src"), src.shape[1], int(q_off), int(k_off), int(v_off), float(q_scale), _ptr(gates, "gates", f32),
+        _ptr(gate_bias, "gate_bias", f32), float(cap), float(guard), _ptr(S, "S", f32), _ptr(z, "z", f32), _ptr(m, "m", f32),
+        _ptr(out, "out", f32), _ptr(row_slot, "row_slot", i32), _ptr(row_q_start, "row_q_start", i32), rows, H, dk, dv,
+        dtype_code(src.dtype), _stream()), "matrix_memory_step")
+    return out
+
+
 def matrix_memory_chunk() -> int:
     """Tokens of a chunk on the path that runs a row's chunks in parallel."""
     return int(_l.load().dk_matrix_memory_chunk())

@@ -8,9 +8,9 @@ With mixer input h, H heads, key size dk and value size dv:
     out = W_o ( o / rms(o per head) * w * sigmoid(W_g h) )
 S [H, dk, dv], z [H, dk] and m [H] start at zero (m too: not at minus infinity), live in 32 bit, one set per run of the layer,
 and are carried from step to step, so a prompt may be cut anywhere.  q, k, v and the output gate are one product; the two
-gates' rows are a second, small product whose sums stay 32 bit.  Steps of short portions and single tokens take the tokens in
-turn, one block per (row, head, slice of the value entries); long portions run their chunks of 32 tokens in parallel
-(``csrc/matrix_memory_chunked.cu``).
+gates' rows are a second, small product whose sums stay 32 bit.  Steps of single tokens stream the memory through registers once, one block per
+(row, head); short portions and mixed steps take a row's tokens in turn, one block per (row, head, slice of the value entries)
+(both in ``csrc/gated_recurrence.cu``); long portions run their chunks of 32 tokens in parallel (``csrc/matrix_memory_chunked.cu``).
 """
 from __future__ import annotations
 
@@ -83,6 +83,9 @@ class MatrixMemory(Mixer):
             work = ctx.scratch("matrix_memory.chunks", (ops.matrix_memory_chunked_work(total, H, dk, dv),), torch.float32, bound=(bound,))
             ops.matrix_memory_chunked(qkvg, 0, H * dk, 2 * H * dk, dk ** -0.5, gates, self.gate_bias, self.cap, self.guard, st[MEMORY],
                                       st[NORMALIZER], st[MAXIMUM], o, work, base, total, most, H=H, dk=dk, dv=dv, **rows)
+        elif ctx.decode_only and ops.matrix_memory_step_supported(dk, dv):
+            ops.matrix_memory_step(qkvg, 0, H * dk, 2 * H * dk, dk ** -0.5, gates, self.gate_bias, self.cap, self.guard, st[MEMORY],
+                                   st[NORMALIZER], st[MAXIMUM], o, H=H, dk=dk, dv=dv, row_slot=ctx.row_slot, row_q_start=ctx.row_q_start)
         else:
             ops.matrix_memory(qkvg, 0, H * dk, 2 * H * dk, dk ** -0.5, gates, self.gate_bias, self.cap, self.guard, st[MEMORY],
                               st[NORMALIZER], st[MAXIMUM], o, H=H, dk=dk, dv=dv, **rows)

@@ -289,7 +289,7 @@ def test_the_memorys_chunks_in_parallel_against_the_tokens_in_turn(sizes, gates)
     want = plain_rows(pieces)
     bias = torch.zeros(2 * H, device=dev)
     results = {}
-    for how in ("in turn", "in parallel", "parallel then turn"):
+    for how in ("in turn", "in turn, sliced", "in parallel", "parallel then turn"):
         S = torch.zeros(rows, H, dk, dv, device=dev)
         z = torch.zeros(rows, H, dk, device=dev)
         m = torch.zeros(rows, H, device=dev)
@@ -311,7 +311,8 @@ def test_the_memorys_chunks_in_parallel_against_the_tokens_in_turn(sizes, gates)
                 ops.matrix_memory_chunked(src, 0, H * dk, 2 * H * dk, dk ** -0.5, g, bias, cap, 1e-6, S, z, m, out, work, base, sum(counts),
                                           max(counts), H=H, dk=dk, dv=dv, **meta)
             else:
-                ops.matrix_memory(src, 0, H * dk, 2 * H * dk, dk ** -0.5, g, bias, cap, 1e-6, S, z, m, out, H=H, dk=dk, dv=dv, **meta)
+                ops.matrix_memory(src, 0, H * dk, 2 * H * dk, dk ** -0.5, g, bias, cap, 1e-6, S, z, m, out, H=H, dk=dk, dv=dv,
+                                  slice_=max(1, dv // 3) if how.endswith("sliced") else None, **meta)
             for i in range(rows):
                 got[i].append(out[starts[i]:starts[i] + lens[i]].cpu().double())
         results[how] = (S.cpu(), z.cpu(), m.cpu())
@@ -322,9 +323,50 @@ def test_the_memorys_chunks_in_parallel_against_the_tokens_in_turn(sizes, gates)
             err = (o - ref).abs().max(dim=1).values
             bad = (err > 2e-5 * ref.abs().max().item() + 1e-6 + 2e-6 * cond * ref.abs().max(dim=1).values).nonzero()
             assert not bad.numel(), f"{how}: row {i} first differs at token {int(bad[0, 0])}: {err[int(bad[0, 0])].item():.3e}"
-    for how in ("in parallel", "parallel then turn"):      # the states the two kernels leave are the same up to rounding
+    for how in ("in turn, sliced", "in parallel", "parallel then turn"):      # the states the two kernels leave are the same up to rounding
         for a, b, name in zip(results["in turn"], results[how], ("memory", "keys' sum", "maximum")):
             assert (a - b).abs().max().item() <= 2e-5 * a.abs().max().item() + 1e-6, f"{how}: the {name} left behind differs"
+
+
+@pytest.mark.parametrize("sizes", [(2, 16, 8), (3, 7, 12), (1, 64, 96), (2, 24, 200)])
+def test_the_memorys_single_tokens(sizes):
+    """The kernel for steps of single tokens against the plain recurrence, 32 bit: 40 steps of four rows whose slots are not in
+    order, one of them with input gates at the cap from its 20th token on."""
+    from delta_b200.kernels import ops
+    H, dk, dv = sizes
+    assert ops.matrix_memory_step_supported(dk, dv)
+    dev = torch.device("cuda:0")
+    gen = torch.Generator().manual_seed(dk * 7 + dv)
+    cap, rows, steps = 10.0, 4, 40
+    stride = 2 * H * dk + H * dv + 3
+    src = torch.randn(steps, rows, stride, generator=gen)
+    g = torch.cat([torch.randn(steps, rows, H, generator=gen) * 2, torch.randn(steps, rows, H, generator=gen) * 2 + 3], dim=2)
+    g[20:, 1, :H] += 25.0
+    S = torch.zeros(rows + 2, H, dk, dv, device=dev)
+    z = torch.zeros(rows + 2, H, dk, device=dev)
+    m = torch.zeros(rows + 2, H, device=dev)
+    slots = torch.tensor([4, 0, 5, 2], dtype=torch.int32, device=dev)
+    starts = torch.arange(rows, dtype=torch.int32, device=dev)
+    bias = torch.zeros(2 * H, device=dev)
+    got = []
+    for t in range(steps):
+        out = torch.full((rows, H * dv), float("nan"), device=dev)
+        ops.matrix_memory_step(src[t].to(dev), 0, H * dk, 2 * H * dk, dk ** -0.5, g[t].to(dev).contiguous(), bias, cap, 1e-6, S, z, m, out,
+                               H=H, dk=dk, dv=dv, row_slot=slots, row_q_start=starts)
+        got.append(out.cpu().double())
+    got = torch.stack(got)       # [steps, rows, H * dv]
+    assert S[1].abs().max().item() == 0 and S[3].abs().max().item() == 0, "a slot of no row was written"
+    for r in range(rows):
+        x, gr = src[:, r].double(), g[:, r].double()
+        q = x[:, :H * dk].view(steps, H, dk) * dk ** -0.5
+        k = x[:, H * dk:2 * H * dk].view(steps, H, dk)
+        v = x[:, 2 * H * dk:2 * H * dk + H * dv].view(steps, H, dv)
+        ref, cond = plain.matrix_memory(q, k, v, plain.capped(gr[:, :H], cap), torch.nn.functional.logsigmoid(plain.capped(gr[:, H:], cap)),
+                                        with_condition=True)
+        ref = ref.reshape(steps, H * dv)
+        err = (got[:, r] - ref).abs().max(dim=1).values
+        bad = (err > 2e-5 * ref.abs().max().item() + 1e-6 + 2e-6 * cond.max(dim=1).values * ref.abs().max(dim=1).values).nonzero()
+        assert not bad.numel(), f"row {r} first differs at step {int(bad[0, 0])}: {err[int(bad[0, 0])].item():.3e}"
 
 
 def test_a_slot_used_again_starts_clean(tmp_path_factory):
