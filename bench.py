@@ -554,8 +554,8 @@ def design_workload(args, design: str) -> int:
                 "rows_append_unit": ((2 * H + 3 * G) * 128 * 2 * T * n_att, 0),
                 "gated_rms_norm": ((H * 128 * 4 + 2 * H * 128 * 2) * T * n_lin, 0),
                 "experts_combine": ((top * d * 4 + 2 * d * 2) * T * n_moe, 0),
-                "decay_attention": (0, 2 * T * H * (2 * 128 * 128 + 16 * (128 + 128)) * n_lin),
-                "experts_gemm": (0, 2 * T * top * 3 * d * F * n_moe),
+                "decay_attention_chunked": (0, 2 * T * H * (2 * 128 * 128 + 16 * (128 + 128)) * n_lin),
+                "experts_gemm_tc": (0, 2 * T * top * 3 * d * F * n_moe),
                 "attention_rows_mma": (0, 4 * 128 * H * (T * (T + 1) // 2) * n_att),
             }
         if design == "pibalorn":
@@ -566,15 +566,16 @@ def design_workload(args, design: str) -> int:
             seen = Wn * T - Wn * (Wn - 1) // 2       # (query, key) pairs inside the window
             work = {
                 "residual_norm": ((2 * d * 4 + 2 * d * 4 + d * 2) * T * (2 * runs), 0),
-                "matrix_memory": (0, 2 * T * H * (2 * 128 * 128 + 16 * (128 + 128)) * n_mem),     # counted as the linear attention's
+                "matrix_memory_chunked": (0, 2 * T * H * (2 * 128 * 128 + 16 * (128 + 128)) * n_mem),     # counted as the linear attention's
                 "gated_rms_norm": ((H * 128 * 4 + 2 * H * 128 * 2) * T * (n_mem + n_pair), 0),
                 "gated_recurrence": ((2 * d * 4 + 3 * d * 2) * T * n_pair, 0),
                 "conv_silu": (2 * d * 2 * T * n_pair, 0),
                 "normed_sum": (3 * d * 4 * T * n_pair, 0),
-                "rows_append": ((2 * H + 4 * G) * 128 * 2 * T * n_pair, 0),
+                "rows_append_unit": ((2 * H + 4 * G) * 128 * 2 * T * n_pair, 0),
+                "sigmoid_gate": (3 * H * 128 * 2 * T * n_pair, 0),
                 "activation": (2 * top * F * 2 * T * n_moe, 0),
                 "experts_combine": ((top * d * 4 + d * 4) * T * n_moe, 0),
-                "experts_gemm": (0, 2 * T * top * 2 * d * F * n_moe),
+                "experts_gemm_tc": (0, 2 * T * top * 2 * d * F * n_moe),
                 "attention_rows_mma": (0, 4 * 128 * H * seen * n_pair),
             }
         yi_work = {
