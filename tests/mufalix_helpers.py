@@ -66,6 +66,10 @@ def config(which: str) -> dict:
         return dict(base, vocab=200, width=128, embedding=dict(scale=2.0), loop=dict(start=0, stop=2, times=2), layers=[   # product
             moe(parallel(left(4, 2, 64, 32, 0.15, window=70, rot_dims=32, base=5000.0, scaling=(2.0, 1.0, 2.0, 128)), 128, 4, 2), 4, 2, 64, 2.0),
             moe(mlstm(2, 64, 64, 10.0), 3, 1, 128)])
+    if which == "larger":   # heads, experts and widths that the tcgen05 products, the warp-MMA attention and the chunked kernels take in long
+        return dict(base, vocab=1000, width=512, embedding=dict(scale=4.0), loop=dict(start=0, stop=2, times=2), layers=[   # portions
+            moe(mlstm(4, 64, 128, 12.0), 8, 2, 256, 2.0),
+            moe(parallel(left(8, 2, 64, 64, 0.125, window=300, rot_dims=32, base=100000.0, scaling=(4.0, 1.0, 4.0, 256)), 512, 4, 4), 8, 2, 256, 1.5)])
     if which == "only_memory":
         return dict(base, vocab=97, width=40, layers=[bare(mlstm(2, 16, 8, 4.0))])
     if which == "only_pair":
@@ -77,7 +81,7 @@ def config(which: str) -> dict:
     raise KeyError(which)
 
 
-PAGE_SIZE = {"wide": 16, "mix": 16, "odd": 2, "one": 4, "sharp": 4, "only_memory": 16, "only_pair": 8, "only_experts": 16, "only_loop": 8}
+PAGE_SIZE = {"larger": 16, "wide": 16, "mix": 16, "odd": 2, "one": 4, "sharp": 4, "only_memory": 16, "only_pair": 8, "only_experts": 16, "only_loop": 8}
 
 
 def make_weights(cfg: dict, seed: int) -> dict:

@@ -137,6 +137,22 @@ def test_every_way_of_cutting(tmp_path_factory, which, dtype):
     print(f"\nworst logit error {which} {dtype}: " + ", ".join(f"{k} {v:.2e}" for k, v in worst.items()))
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_larger_sizes(tmp_path_factory, dtype):
+    """Width 512, 8 experts, heads of 64 and 128: a 700-token prompt whole (about 175 rows an expert: the tcgen05 products; the
+    memory's chunks and the recurrence's segments in parallel; the library's batched product for the gates), in portions of 256
+    beside a second request, and its last tokens one by one."""
+    cfg, W, folder = model(tmp_path_factory, "larger")
+    lengths = [700, 130]
+    toks = [helpers.random_tokens(n, cfg["vocab"], 900 + i) for i, n in enumerate(lengths)]
+    refs = [plain.forward(cfg, W, t)[0] for t in toks]
+    noise = rounding_noise(cfg, W, toks, refs) if dtype == "bfloat16" else None
+    runner = make_runner(folder, "larger", dtype, max_batch=2, max_seq_len=704, max_tokens_per_step=1024)
+    compare(helpers.run_schedule(runner, toks, helpers.whole(lengths)), refs, lengths, dtype, "whole", noise)
+    steps = [[(0, 0, 256), (1, 0, 100)], [(0, 256, 256), (1, 100, 1)], [(0, 512, 180), (1, 101, 29)]] + [[(0, p, 1)] for p in range(692, 700)]
+    compare(helpers.run_schedule(runner, toks, steps), refs, lengths, dtype, "portions of 256 beside a second request", noise)
+
+
 @pytest.mark.parametrize("which", ["mix", "odd", "one", "only_memory", "only_pair", "only_experts", "only_loop"])
 def test_stream_after_every_layer_run(tmp_path_factory, which):
     """32 bit: the residual stream after every run of a layer, for a prompt in one step and for the same prompt cut in two."""

@@ -9,7 +9,7 @@ import torch
 import mufalix_helpers as mh
 import plain_mufalix as plain
 
-ALL = ["wide", "mix", "odd", "one", "sharp", "only_memory", "only_pair", "only_experts", "only_loop"]
+ALL = ["larger", "wide", "mix", "odd", "one", "sharp", "only_memory", "only_pair", "only_experts", "only_loop"]
 F = torch.float64
 
 
