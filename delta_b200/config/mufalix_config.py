@@ -15,7 +15,7 @@ Mixer kinds and their keys:
     parallel    left  {heads, kv_heads, dim, vdim, scale, mask {size} (absent: every earlier token is seen),
                        rot {base, dims, scaling {factor, low, high, original} (absent: unscaled)} (absent: no rotation)}
                 right {width, conv, blocks}
-Feed-forward kinds:
+Feed-forward kinds (``kind``; absent: moe):
     moe         router {experts, top, scale (absent: 1)}, expert {ff}
 """
 from __future__ import annotations
@@ -90,7 +90,7 @@ class MufalixConfig:
             mlp = L.get("mlp")
             if mlp is not None:
                 mlp = dict(mlp)
-                mk = need(mlp, "kind", f"mlp of layer {i}")
+                mk = mlp.get("kind") or "moe"      # the design has one kind of feed-forward
                 if mk != "moe":
                     raise ConfigError(f"layer {i}: unknown feed-forward kind '{mk}' (moe)")
                 r = need(mlp, "router", f"mlp of layer {i}")

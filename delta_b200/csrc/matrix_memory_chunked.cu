@@ -351,13 +351,9 @@ extern "C" int dk_matrix_memory_chunked_supported(int dk, int dv) {
   return mmc_out_smem(dk, mmc_slice(dv)) <= MMC_SMEM_LIMIT && mmc_state_smem(dk, mmc_slice(dv)) <= MMC_SMEM_LIMIT;
 }
 
-// Floats of `work` for `total_chunks` chunks: every chunk's memory, keys' sum and four numbers.
-extern "C" long long dk_matrix_memory_chunked_work(long long total_chunks, int H, int dk, int dv) {
-  return total_chunks * H * ((long long)dk * dv + dk + 4);
-}
-
 // `chunk_base` [rows]: the number of chunks (of dk_matrix_memory_chunk() tokens) of all rows before this one; `total_chunks`: of all
-// rows; `max_chunks`: the most of any row.  The other arguments are dk_matrix_memory's.
+// rows; `max_chunks`: the most of any row; `work`: total_chunks * H * (dk * dv + dk + 4) floats (every chunk's memory, keys' sum and
+// four numbers).  The other arguments are dk_matrix_memory's.
 extern "C" int dk_matrix_memory_chunked(const void* src, int src_stride, int q_off, int k_off, int v_off, float q_scale, const float* gates,
                                         const float* gate_bias, float cap, float guard, float* S_state, float* z_state, float* m_state,
                                         float* out, float* work, const int* row_slot, const int* row_q_start, const int* row_q_len,

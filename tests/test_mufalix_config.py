@@ -172,3 +172,12 @@ def test_plain_router_correction_enters_the_choice_only():
     picked = torch.gather(s, 1, choice)
     assert torch.allclose(weight, picked / picked.sum(-1, keepdim=True) * 2.5)
     assert torch.allclose(weight.sum(-1), torch.full((5,), 2.5, dtype=F))
+
+
+def test_a_feed_forward_without_a_kind_is_a_mixture():
+    from delta_b200.config.mufalix_config import MufalixConfig
+    cfg = mh.config("only_experts")
+    for L in cfg["layers"]:
+        L["mlp"].pop("kind")
+    got = MufalixConfig.from_dict(cfg)
+    assert got.layers[0].mlp["router"]["experts"] == 7
