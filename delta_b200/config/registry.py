@@ -11,7 +11,7 @@ from __future__ import annotations
 import json
 from dataclasses import dataclass
 from pathlib import Path
-from typing import Callable, Dict
+from typing import Callable, Dict, Optional
 
 from .model_config import ConfigError
 
@@ -21,13 +21,15 @@ class Architecture:
     name: str
     config_from_dict: Callable  # dict of config.json -> typed configuration
     build_spec: Callable        # (configuration, EngineConfig) -> ModelSpec
+    sizes_from_shapes: Optional[Callable] = None   # (dict of config.json, {tensor name: shape}) -> dict with the sizes filled in that
+                                                   # config.json leaves to the tensors' shapes (None: config.json says everything)
 
 
 ARCHITECTURES: Dict[str, Architecture] = {}
 
 
-def register_architecture(name: str, config_from_dict: Callable, build_spec: Callable) -> None:
-    ARCHITECTURES[name] = Architecture(name, config_from_dict, build_spec)
+def register_architecture(name: str, config_from_dict: Callable, build_spec: Callable, sizes_from_shapes: Optional[Callable] = None) -> None:
+    ARCHITECTURES[name] = Architecture(name, config_from_dict, build_spec, sizes_from_shapes)
 
 
 def unregister_architecture(name: str) -> None:
@@ -53,4 +55,12 @@ def read_config(folder):
         raise ConfigError(f"no config.json in {folder}")
     raw = json.loads(path.read_text())
     arch = architecture_of(raw)
+    if arch.sizes_from_shapes is not None:
+        from ..weights.safetensors_io import open_model_files
+        shapes = {}
+        for f in open_model_files(folder):
+            for n in f.names():
+                shapes[n] = tuple(f.info(n)[0])
+            f.close()
+        raw = arch.sizes_from_shapes(raw, shapes)
     return arch, arch.config_from_dict(raw)

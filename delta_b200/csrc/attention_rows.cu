@@ -6,6 +6,8 @@
 // kernels of this family are checked against it.
 //
 //   s_j  = (q . k_j) * scale          for the visible keys  max(0, i - window + 1) <= j <= i
+//   s_j <- softcap * tanh(s_j / softcap)                      (softcap > 0)
+//   s_j <- s_j + dist_bias[min(i - j, dist_max)][h]           (a table of biases by distance, one column a head)
 //   p_j  = exp(s_j) / (sum_j' exp(s_j') [+ exp(sink_h)])
 //   y    = sum_j p_j v_j
 #include "common.cuh"
@@ -63,6 +65,8 @@ __global__ void __launch_bounds__(CH) attention_rows_plain_kernel(const DkRowAtt
           float d = 0.f;
           for (int i = 0; i < dk; ++i) d = fmaf(qs[i], to_f32<T>(kr[i]), d);
           s = d * p.scale;
+          if (p.softcap > 0.f) s = p.softcap * tanhf(s / p.softcap);
+          if (p.dist_bias != nullptr) s += p.dist_bias[(size_t)min(pos - key, p.dist_max) * p.H + h];
           vo = (long long)(base + p.v_off);
         }
       }
@@ -171,15 +175,18 @@ __global__ void rows_append_kernel(T* __restrict__ src, int src_stride, const in
 // not), and rounded once.  q goes back in place, k to the cache row.  value_from_key: the value is the key as
 // projected, before rotation and norm (its first dv entries), so no v is read.  bias (32 bit, laid out as a row of src) is
 // added to q, k and v as they are read.  q_norm / k_norm [dk]: before the rotation the head is RMS-normed with this
-// weight, x / sqrt(mean(x^2) + pre_eps) * w, the same weight for every head.
+// weight, x / sqrt(mean(x^2) + pre_eps) * w, the same weight for every head; norm_whole: the mean is taken over all columns of
+// q (and of k) at once and the weights are [H*dk] and [KV*dk].  temp_every > 0: the query is multiplied by
+// 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1).  KV may be 0 (no cache): src holds queries only.
 template <typename T>
 __global__ void rows_append_unit_kernel(T* __restrict__ src, int src_stride, const int* __restrict__ tok_pos, const int* __restrict__ tok_row,
                                         const int* __restrict__ block_table, int max_pages, T* __restrict__ cache, int num_pages,
                                         const float* __restrict__ table, int table_positions, int rot_dims, int interleaved, int H,
                                         int KV, int dk, int dv, int ps, int row_width, int k_off, int v_off, int unit_norm, float eps,
                                         int value_from_key, const float* __restrict__ bias, const float* __restrict__ q_norm,
-                                        const float* __restrict__ k_norm, float pre_eps, int* err) {
-  extern __shared__ float heads[];     // [warps][dk]
+                                        const float* __restrict__ k_norm, float pre_eps, int norm_whole, float temp_coef, int temp_every,
+                                        int* err) {
+  extern __shared__ float heads[];     // [warps][dk] (norm_whole: and 34 behind them)
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const int pos = tok_pos[t], b = tok_row[t];
   T* base = src + (size_t)t * src_stride;
@@ -191,6 +198,22 @@ __global__ void rows_append_unit_kernel(T* __restrict__ src, int src_stride, con
   const long long page = at >= 0 ? at / ps : 0, off = at >= 0 ? at % ps : 0;
   const int half = rot_dims / 2;
   float* x = heads + (size_t)warp * dk;
+  float whole_q = 0.f, whole_k = 0.f;      // norm_whole: 1 / rms over all of q's columns, and over all of k's
+  if (norm_whole) {
+    float* scratch = heads + (size_t)warps * dk;
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < (H + KV) * dk; i += blockDim.x) {
+      const float v = to_f32<T>(base[i]) + (bias != nullptr ? bias[i] : 0.f);
+      if (i < H * dk) sq += v * v;
+      else sk += v * v;
+    }
+    sq = block_sum(sq, scratch);
+    sk = block_sum(sk, scratch);
+    whole_q = 1.f / sqrtf(sq / (float)(H * dk) + pre_eps);
+    if (KV > 0) whole_k = 1.f / sqrtf(sk / (float)(KV * dk) + pre_eps);
+  }
+  // the factor on a query by its position: 1 + coef * ln(floor((pos + 1) / every) + 1)
+  const float temp = temp_every > 0 ? 1.f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.f) : 1.f;
   for (int hs = warp; hs < H + KV; hs += warps) {
     T* hp = base + (size_t)hs * dk;
     const bool is_key = hs >= H;
@@ -204,9 +227,10 @@ __global__ void rows_append_unit_kernel(T* __restrict__ src, int src_stride, con
       if (crow != nullptr && value_from_key && i < dv) crow[v_off + i] = bias != nullptr ? from_f32<T>(v) : raw;
     }
     const float* pre_w = is_key ? k_norm : q_norm;
-    if (pre_w != nullptr) {      // the RMS norm with a weight, before the rotation
-      const float pre = 1.f / sqrtf(warp_sum(ss0) / (float)dk + pre_eps);
-      for (int i = lane; i < dk; i += 32) x[i] = x[i] * pre * pre_w[i];
+    if (pre_w != nullptr) {      // the RMS norm with a weight, before the rotation: over the head, or over all heads at once
+      const float pre = norm_whole ? (is_key ? whole_k : whole_q) : 1.f / sqrtf(warp_sum(ss0) / (float)dk + pre_eps);
+      const float* w = norm_whole ? pre_w + (size_t)(is_key ? hs - H : hs) * dk : pre_w;
+      for (int i = lane; i < dk; i += 32) x[i] = x[i] * pre * w[i];
     }
     __syncwarp();
     if (table != nullptr) {
@@ -228,6 +252,7 @@ __global__ void rows_append_unit_kernel(T* __restrict__ src, int src_stride, con
       ss = warp_sum(ss);
       inv = 1.f / sqrtf(ss / (float)dk + eps);
     }
+    if (!is_key) inv *= temp;
     for (int i = lane; i < dk; i += 32) {
       const T r = from_f32<T>(x[i] * inv);
       if (!is_key) hp[i] = r;
@@ -250,12 +275,14 @@ __global__ void rows_append_unit_kernel(T* __restrict__ src, int src_stride, con
 //   k_rot  rotated on its first rot_dims entries                 -> cache row [R, R + dr)
 //   q_rot  of every head rotated                                  -> qabs[t][h][R, R + dr)
 // The front part qabs[t][h][0, R) is filled by the product of q_plain with the key up-projection.
+// low_src != nullptr: [low | k_rot] of token t lies at low_src + t * low_stride instead (queries that were made by a
+// product of their own, from a latent), and src holds the heads' queries only.
 template <typename T>
 __global__ void latent_prepare_kernel(const T* __restrict__ src, int src_stride, const int* __restrict__ tok_pos,
                                       const int* __restrict__ tok_row, const int* __restrict__ block_table, int max_pages,
                                       T* __restrict__ cache, int num_pages, const float* __restrict__ table, int table_positions,
                                       int rot_dims, int interleaved, const float* __restrict__ w, float eps, T* __restrict__ qabs,
-                                      int H, int dq, int dr, int R, int ps, int* err) {
+                                      int H, int dq, int dr, int R, int ps, const T* __restrict__ low_src, int low_stride, int* err) {
   __shared__ float scratch[34];
   const int t = blockIdx.x;
   const int pos = tok_pos[t], b = tok_row[t];
@@ -264,7 +291,7 @@ __global__ void latent_prepare_kernel(const T* __restrict__ src, int src_stride,
     return;
   }
   const T* base = src + (size_t)t * src_stride;
-  const T* low = base + (size_t)H * (dq + dr);
+  const T* low = low_src != nullptr ? low_src + (size_t)t * low_stride : base + (size_t)H * (dq + dr);
   const int width = R + dr;
   const long long at = cache != nullptr ? row_slot_of(block_table, max_pages, num_pages, b, pos, ps, t, err) : -1;
   T* crow = at >= 0 ? cache + (size_t)at * width : nullptr;
@@ -352,21 +379,25 @@ extern "C" int dk_rows_append_unit(void* src, int src_stride, const int* tok_pos
                                    int max_pages, void* cache, int num_pages, const float* table, int table_positions, int rot_dims,
                                    int interleaved, int T_, int H, int KV, int dk, int dv, int ps, int row_width, int k_off, int v_off,
                                    int unit_norm, float eps, int value_from_key, const float* bias, const float* q_norm,
-                                   const float* k_norm, float pre_eps, int dtype, int* err, cudaStream_t stream) {
+                                   const float* k_norm, float pre_eps, int norm_whole, float temp_coef, int temp_every, int dtype,
+                                   int* err, cudaStream_t stream) {
   if (T_ == 0) return 0;
-  DK_REQUIRE(T_ > 0 && H > 0 && KV > 0 && dk > 0 && dv > 0 && ps > 0, "rows_append_unit: bad sizes T=%d H=%d KV=%d dk=%d dv=%d ps=%d", T_, H, KV, dk, dv, ps);
+  DK_REQUIRE(T_ > 0 && H > 0 && KV >= 0 && dk > 0 && dv > 0 && ps > 0, "rows_append_unit: bad sizes T=%d H=%d KV=%d dk=%d dv=%d ps=%d", T_, H, KV, dk, dv, ps);
+  DK_REQUIRE(KV > 0 || cache == nullptr, "rows_append_unit: a cache is given and no keys to append");
+  DK_REQUIRE(!norm_whole || q_norm != nullptr, "rows_append_unit: a norm over all heads needs its weights");
+  DK_REQUIRE(temp_every >= 0, "rows_append_unit: bad temperature period %d", temp_every);
   DK_REQUIRE(src_stride >= (H + KV) * dk + (value_from_key ? 0 : KV * dv), "rows_append_unit: rows of %d elements do not hold q, k and v", src_stride);
   DK_REQUIRE(!value_from_key || dv <= dk, "rows_append_unit: a value of %d entries cannot be taken from a key of %d", dv, dk);
   DK_REQUIRE(cache == nullptr || (block_table != nullptr && max_pages > 0 && num_pages > 0), "rows_append_unit: a cache is given without a block table");
   DK_REQUIRE(table == nullptr || (rot_dims > 0 && rot_dims % 2 == 0 && rot_dims <= dk), "rows_append_unit: %d rotated entries do not fit a head of %d", rot_dims, dk);
   DK_REQUIRE(k_off + dk <= row_width && v_off + dv <= row_width, "rows_append_unit: key and value do not fit a row of %d", row_width);
   const int threads = (H + KV) >= 8 ? 256 : 128;
-  const size_t smem = (size_t)(threads / 32) * dk * sizeof(float);
+  const size_t smem = ((size_t)(threads / 32) * dk + 34) * sizeof(float);
   DK_REQUIRE(smem <= 48 * 1024, "rows_append_unit: heads of %d entries do not fit the shared memory", dk);
 #define LAUNCH(T)                                                                                                                 \
   rows_append_unit_kernel<T><<<T_, threads, smem, stream>>>((T*)src, src_stride, tok_pos, tok_row, block_table, max_pages, (T*)cache, \
                                                             num_pages, table, table_positions, rot_dims, interleaved, H, KV, dk, dv, \
-                                                            ps, row_width, k_off, v_off, unit_norm, eps, value_from_key, bias, q_norm, k_norm, pre_eps, err)
+                                                            ps, row_width, k_off, v_off, unit_norm, eps, value_from_key, bias, q_norm, k_norm, pre_eps, norm_whole, temp_coef, temp_every, err)
   if (dtype == DK_F32) LAUNCH(float);
   else if (dtype == DK_BF16) LAUNCH(__nv_bfloat16);
   else DK_REQUIRE(false, "rows_append_unit: unknown dtype %d", dtype);
@@ -377,17 +408,18 @@ extern "C" int dk_rows_append_unit(void* src, int src_stride, const int* tok_pos
 extern "C" int dk_latent_prepare(const void* src, int src_stride, const int* tok_pos, const int* tok_row, const int* block_table,
                                  int max_pages, void* cache, int num_pages, const float* table, int table_positions,
                                  int rot_dims, int interleaved, const float* w, float eps, void* qabs, int T_, int H, int dq,
-                                 int dr, int R, int ps, int dtype, int* err, cudaStream_t stream) {
+                                 int dr, int R, int ps, const void* low_src, int low_stride, int dtype, int* err, cudaStream_t stream) {
   if (T_ == 0) return 0;
   DK_REQUIRE(T_ > 0 && H > 0 && dq > 0 && dr >= 0 && R > 0 && ps > 0, "latent_prepare: bad sizes T=%d H=%d dq=%d dr=%d R=%d ps=%d", T_, H, dq, dr, R, ps);
-  DK_REQUIRE(src_stride >= H * (dq + dr) + R + dr, "latent_prepare: rows of %d elements do not hold the queries and the latent", src_stride);
+  DK_REQUIRE(src_stride >= H * (dq + dr) + (low_src == nullptr ? R + dr : 0), "latent_prepare: rows of %d elements do not hold the queries and the latent", src_stride);
+  DK_REQUIRE(low_src == nullptr || low_stride >= R + dr, "latent_prepare: rows of %d elements do not hold the latent", low_stride);
   DK_REQUIRE(cache == nullptr || (block_table != nullptr && max_pages > 0 && num_pages > 0), "latent_prepare: a cache is given without a block table");
   DK_REQUIRE(table == nullptr || (rot_dims > 0 && rot_dims % 2 == 0 && rot_dims <= dr), "latent_prepare: %d rotated entries do not fit a part of %d", rot_dims, dr);
   const int threads = 256;
 #define LAUNCH(T)                                                                                                         \
   latent_prepare_kernel<T><<<T_, threads, 0, stream>>>((const T*)src, src_stride, tok_pos, tok_row, block_table, max_pages, \
                                                         (T*)cache, num_pages, table, table_positions, rot_dims, interleaved, \
-                                                        w, eps, (T*)qabs, H, dq, dr, R, ps, err)
+                                                        w, eps, (T*)qabs, H, dq, dr, R, ps, (const T*)low_src, low_stride, err)
   if (dtype == DK_F32) LAUNCH(float);
   else if (dtype == DK_BF16) LAUNCH(__nv_bfloat16);
   else DK_REQUIRE(false, "latent_prepare: unknown dtype %d", dtype);

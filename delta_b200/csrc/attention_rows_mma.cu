@@ -8,8 +8,9 @@
 // tiles (cp.async, two stages, 16-byte chunks swizzled for ldmatrix); a cached row holds key and value, so one
 // copy brings both, and a value that is the front of its key is not copied twice.  Per tile and warp:
 // S = Q K^T (mma.sync.m16n8k16, float accumulators), mask by position (causal, window), online softmax in
-// float, O += P V with P split into two bfloat16 parts (so the softmax weights keep 16 bits of mantissa; their sum
-// is taken in float from the unrounded weights).  The sink joins the denominator when the result is finished.
+// float (scores may first be capped, s <- cap tanh(s / cap), and take a bias by distance and head), O += P V
+// with P split into two bfloat16 parts (so the softmax weights keep 16 bits of mantissa; their sum is taken in
+// float from the unrounded weights).  The sink joins the denominator when the result is finished.
 //
 // grid (tiles of query rows, splits, batch rows * KV).  With more than one split each block takes a share of the
 // key tiles and stores (unnormalised O, running maximum, sum) per query row; a second kernel merges them.
@@ -86,6 +87,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_mma_kernel(const Dk
   float o[RM][NT][4];
   float m_run[RM][2], l_run[RM][2];
   int pos_r[RM][2];     // positions of this thread's query rows: rows warp*WR + rm*16 + gq and + 8
+  int head_r[RM][2];    // and their heads
+  const bool shaped = p.softcap > 0.f || p.dist_bias != nullptr;
 #pragma unroll
   for (int rm = 0; rm < RM; ++rm) {
 #pragma unroll
@@ -94,6 +97,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_mma_kernel(const Dk
     l_run[rm][0] = l_run[rm][1] = 0.f;
     pos_r[rm][0] = pos_start + (m0 + min(warp * WR + rm * 16 + gq, nrows - 1)) / G;
     pos_r[rm][1] = pos_start + (m0 + min(warp * WR + rm * 16 + gq + 8, nrows - 1)) / G;
+    head_r[rm][0] = g * G + (m0 + min(warp * WR + rm * 16 + gq, nrows - 1)) % G;
+    head_r[rm][1] = g * G + (m0 + min(warp * WR + rm * 16 + gq + 8, nrows - 1)) % G;
   }
   const float sc_log2 = p.scale * LOG2E;
   const int warp_first_pos = pos_start + (m0 + min(warp * WR, nrows - 1)) / G;
@@ -148,7 +153,24 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_mma_kernel(const Dk
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
             const int key = kt0 + j * 8 + 2 * tq + c;
-            float v0 = s[rm][j][c] * sc_log2, v1 = s[rm][j][2 + c] * sc_log2;
+            float v0, v1;
+            if (shaped) {      // capped scores and biases by distance: in natural units first
+              v0 = s[rm][j][c] * p.scale;
+              v1 = s[rm][j][2 + c] * p.scale;
+              if (p.softcap > 0.f) {
+                v0 = p.softcap * tanhf(v0 / p.softcap);
+                v1 = p.softcap * tanhf(v1 / p.softcap);
+              }
+              if (p.dist_bias != nullptr) {
+                v0 += p.dist_bias[(size_t)min(max(pos_r[rm][0] - key, 0), p.dist_max) * p.H + head_r[rm][0]];
+                v1 += p.dist_bias[(size_t)min(max(pos_r[rm][1] - key, 0), p.dist_max) * p.H + head_r[rm][1]];
+              }
+              v0 *= LOG2E;
+              v1 *= LOG2E;
+            } else {
+              v0 = s[rm][j][c] * sc_log2;
+              v1 = s[rm][j][2 + c] * sc_log2;
+            }
             if (key > pos_r[rm][0] || (p.window > 0 && key <= pos_r[rm][0] - p.window)) v0 = -INFINITY;
             if (key > pos_r[rm][1] || (p.window > 0 && key <= pos_r[rm][1] - p.window)) v1 = -INFINITY;
             s[rm][j][c] = v0;

@@ -147,14 +147,16 @@ __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, flo
   }
 }
 
-// The gated activation with clamped branches:  g' sigmoid(alpha g') (u' + shift),  g' = min(g, limit), u' = clamp(u, -limit, limit)
-// (limit < 0: nothing is clamped).
-__device__ __forceinline__ float dk_glu_value(float g, float u, float limit, float alpha, float shift) {
+// The gated activation with clamped branches:  g' sigmoid(alpha (g' + cubic g'^3)) (u' + shift),  g' = min(g, limit),
+// u' = clamp(u, -limit, limit) (limit < 0: nothing is clamped).  alpha 1: silu(g) u;  alpha 2 sqrt(2 / pi) with cubic 0.044715: the
+// tanh form of gelu, since 0.5 (1 + tanh z) = sigmoid(2 z).
+__device__ __forceinline__ float dk_glu_value(float g, float u, float limit, float alpha, float shift, float cubic = 0.f) {
   if (limit >= 0.f) {
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
   }
-  return g * (1.f / (1.f + expf(-alpha * g))) * (u + shift);
+  const float z = cubic != 0.f ? g + cubic * g * g * g : g;
+  return g * (1.f / (1.f + expf(-alpha * z))) * (u + shift);
 }
 
 // Eight neighbouring entries from floats (rounded once); p is 16-byte aligned.

@@ -179,6 +179,41 @@ extern "C" int dk_rms_norm(void* x, const void* add, const void* w, void* out, c
   return dk_check_launch("rms_norm");
 }
 
+// The norm of the first d columns of rows that lie `ld` elements apart (a slice of a wider product's result):
+// out[r] = x[r][0:d] * rsqrt(mean(x[r][0:d]^2) + eps) * w, statistics and weight in float, rounded once.
+template <typename T, typename W>
+__global__ void rms_norm_strided_kernel(const T* __restrict__ x, int ld, const W* __restrict__ w, T* __restrict__ out, int d, float eps) {
+  extern __shared__ float row[];  // d floats + 33 for the reduction
+  float* scratch = row + d;
+  const T* xs = x + (size_t)blockIdx.x * ld;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float v = to_f32<T>(xs[i]);
+    row[i] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.f / sqrtf(ss / (float)d + eps);
+  T* o = out + (size_t)blockIdx.x * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_f32<T>(row[i] * inv * to_f32<W>(w[i]));
+}
+
+extern "C" int dk_rms_norm_strided(const void* x, int ld, const void* w, void* out, int n_rows, int d, float eps, int dtype, int w_dtype,
+                                   cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  DK_REQUIRE(n_rows > 0 && d > 0 && ld >= d, "rms_norm_strided: bad sizes rows=%d d=%d ld=%d", n_rows, d, ld);
+  DK_REQUIRE(d <= 12000, "rms_norm_strided: width %d is above the 12000 this kernel keeps in shared memory", d);
+  const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+  const size_t smem = (size_t)(d + 33) * sizeof(float);
+#define LAUNCH(T, W) rms_norm_strided_kernel<T, W><<<n_rows, threads, smem, stream>>>((const T*)x, ld, (const W*)w, (T*)out, d, eps)
+  if (dtype == DK_F32 && w_dtype == DK_F32) LAUNCH(float, float);
+  else if (dtype == DK_BF16 && w_dtype == DK_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else if (dtype == DK_BF16 && w_dtype == DK_F32) LAUNCH(__nv_bfloat16, float);
+  else DK_REQUIRE(false, "rms_norm_strided: unsupported dtypes x=%d w=%d", dtype, w_dtype);
+#undef LAUNCH
+  return dk_check_launch("rms_norm_strided");
+}
+
 // ------------------------------------------------------------- SwiGLU gate
 // gu[t, 0:I] = gate, gu[t, I:2I] = up;  out[t, i] = silu(gate) * up
 // (reference: model.py:514; computed in float, rounded once)

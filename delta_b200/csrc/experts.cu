@@ -1,6 +1,6 @@
 // A mixture of small feed-forward experts, and the gated activation its experts and dense layers share.
 //
-//   glu_clamped     y = g' * sigmoid(alpha g') * (u' + shift),  g' = min(g, limit), u' = clamp(u, -limit, limit)
+//   glu_clamped     y = g' * sigmoid(alpha (g' + cubic g'^3)) * (u' + shift),  g' = min(g, limit), u' = clamp(u, -limit, limit)
 //                   from rows [g (F) | u (F)] (limit < 0: nothing is clamped);
 //   router          per token the router's logits z = W x in 32 bit, the `top` largest of the E experts' logits (the lowest
 //                   index among equals) and the softmax over the chosen logits only (router_topk: the choice alone, from
@@ -28,22 +28,26 @@ constexpr int GEMM_THREADS = 256;
 constexpr int MAX_TOP = 32;
 constexpr int MAX_EXPERTS = 1024;
 
-__device__ __forceinline__ float glu_value(float g, float u, float limit, float alpha, float shift) { return dk_glu_value(g, u, limit, alpha, shift); }
+__device__ __forceinline__ float glu_value(float g, float u, float limit, float alpha, float shift, float cubic = 0.f) {
+  return dk_glu_value(g, u, limit, alpha, shift, cubic);
+}
 
 template <typename T>
-__global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ y, long long rows, int F, float limit, float alpha, float shift) {
+__global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ y, long long rows, int F, float limit, float alpha, float shift,
+                                   float cubic) {
   const long long n = rows * F;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (long long)gridDim.x * blockDim.x) {
     const long long r = idx / F;
     const int i = (int)(idx - r * F);
     const T* row = gu + r * 2 * F;
-    y[idx] = from_f32<T>(glu_value(to_f32<T>(row[i]), to_f32<T>(row[F + i]), limit, alpha, shift));
+    y[idx] = from_f32<T>(glu_value(to_f32<T>(row[i]), to_f32<T>(row[F + i]), limit, alpha, shift, cubic));
   }
 }
 
 // The same for F a multiple of 8 and 16-byte aligned rows: eight entries a thread, 16-byte accesses.
 template <typename T>
-__global__ void glu_clamped_vec_kernel(const T* __restrict__ gu, T* __restrict__ y, long long rows, int F, float limit, float alpha, float shift) {
+__global__ void glu_clamped_vec_kernel(const T* __restrict__ gu, T* __restrict__ y, long long rows, int F, float limit, float alpha, float shift,
+                                       float cubic) {
   const int per_row = F / 8;
   const long long n = rows * per_row;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (long long)gridDim.x * blockDim.x) {
@@ -53,7 +57,7 @@ __global__ void glu_clamped_vec_kernel(const T* __restrict__ gu, T* __restrict__
     load8<T>(gu + r * 2 * F + i, g);
     load8<T>(gu + r * 2 * F + F + i, u);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) o[e] = glu_value(g[e], u[e], limit, alpha, shift);
+    for (int e = 0; e < 8; ++e) o[e] = glu_value(g[e], u[e], limit, alpha, shift, cubic);
     store8<T>(y + r * F + i, o);
   }
 }
@@ -100,8 +104,8 @@ __device__ void pick_top(float* z, int E, int top, int* __restrict__ choice, flo
 
 // The choice by sigmoid scores: `pick` [E] holds score + correction and is used up, `score` [E] the scores s = sigmoid(z).  The
 // `top` largest of pick are chosen (the lowest index among equals); a chosen expert's weight is its score without the
-// correction, divided by the sum of the chosen scores (+ 1e-20), times `scale`.
-__device__ void pick_top_scored(float* pick, const float* score, int E, int top, float scale, int* __restrict__ choice,
+// correction, divided by the sum of the chosen scores (+ 1e-20) when `normalize`, times `scale`.
+__device__ void pick_top_scored(float* pick, const float* score, int E, int top, float scale, int normalize, int* __restrict__ choice,
                                 float* __restrict__ weight, int lane) {
   float sum = 0.f, my_weight = 0.f;
   int my_choice = -1;
@@ -136,7 +140,7 @@ __device__ void pick_top_scored(float* pick, const float* score, int E, int top,
   }
   if (lane < top) {
     choice[lane] = my_choice;
-    weight[lane] = my_weight / (sum + 1e-20f) * scale;
+    weight[lane] = (normalize ? my_weight / (sum + 1e-20f) : my_weight) * scale;
   }
 }
 
@@ -215,10 +219,11 @@ router_kernel(const T* __restrict__ x, const T* __restrict__ w, float* __restric
     for (int e = lane; e < E; e += 32) {
       const float sc = 1.f / (1.f + expf(-z[e]));
       score[e] = sc;
-      z[e] = sc + (correction != nullptr ? correction[e] : 0.f);
+      // without a correction the logits themselves are compared: the same order, and no ties where the sigmoid saturates
+      if (correction != nullptr) z[e] = sc + correction[e];
     }
     __syncwarp();
-    pick_top_scored(z, score, E, top, route_scale, choice + (size_t)t * top, weight + (size_t)t * top, lane);
+    pick_top_scored(z, score, E, top, route_scale, scored == 1, choice + (size_t)t * top, weight + (size_t)t * top, lane);
   } else {
     pick_top(z, E, top, choice + (size_t)t * top, weight + (size_t)t * top, lane);
   }
@@ -492,6 +497,17 @@ __global__ void experts_gather_kernel(const __nv_bfloat16* __restrict__ x, const
   for (int c = threadIdx.x; c < K / 8; c += blockDim.x) dst[c] = src ? src[c] : make_uint4(0u, 0u, 0u, 0u);
 }
 
+// xs[t * top + j] = weight[t][j] * x[t], rounded once: the experts' inputs when a choice's weight multiplies what the expert
+// reads (not what it gives).
+template <typename T>
+__global__ void experts_scale_rows_kernel(const T* __restrict__ x, const float* __restrict__ weight, T* __restrict__ xs, int d) {
+  const size_t slot = (size_t)blockIdx.x * gridDim.y + blockIdx.y;      // grid (T, top)
+  const T* src = x + (size_t)blockIdx.x * d;
+  T* dst = xs + slot * d;
+  const float wt = weight[slot];
+  for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = from_f32<T>(wt * to_f32<T>(src[i]));
+}
+
 template <typename T>
 __global__ void experts_combine_kernel(const float* __restrict__ z, const float* __restrict__ weight, int top, const T* __restrict__ shared,
                                        const float* __restrict__ gate_logit, int gate_stride, T* __restrict__ out, int d) {
@@ -500,7 +516,7 @@ __global__ void experts_combine_kernel(const float* __restrict__ z, const float*
   if (shared != nullptr) gate = gate_logit != nullptr ? 1.f / (1.f + expf(-gate_logit[(size_t)t * gate_stride])) : 1.f;
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float a = 0.f;
-    for (int j = 0; j < top; ++j) a = fmaf(weight[(size_t)t * top + j], z[((size_t)t * top + j) * d + i], a);
+    for (int j = 0; j < top; ++j) a = fmaf(weight != nullptr ? weight[(size_t)t * top + j] : 1.f, z[((size_t)t * top + j) * d + i], a);
     if (shared != nullptr) a = fmaf(gate, to_f32<T>(shared[(size_t)t * d + i]), a);
     out[(size_t)t * d + i] = from_f32<T>(a);
   }
@@ -509,7 +525,7 @@ __global__ void experts_combine_kernel(const float* __restrict__ z, const float*
 
 extern "C" int dk_experts_tile_rows() { return TILE_M; }
 
-extern "C" int dk_glu_clamped(const void* gu, void* y, long long rows, int F, float limit, float alpha, float shift, int dtype,
+extern "C" int dk_glu_clamped(const void* gu, void* y, long long rows, int F, float limit, float alpha, float shift, float cubic, int dtype,
                               cudaStream_t stream) {
   if (rows == 0) return 0;
   DK_REQUIRE(rows > 0 && F > 0, "glu_clamped: bad sizes rows=%lld F=%d", rows, F);
@@ -520,8 +536,8 @@ extern "C" int dk_glu_clamped(const void* gu, void* y, long long rows, int F, fl
   if (blocks > most) blocks = most;
 #define LAUNCH(T)                                                                                                              \
   do {                                                                                                                         \
-    if (vec) glu_clamped_vec_kernel<T><<<(int)blocks, 256, 0, stream>>>((const T*)gu, (T*)y, rows, F, limit, alpha, shift);   \
-    else glu_clamped_kernel<T><<<(int)blocks, 256, 0, stream>>>((const T*)gu, (T*)y, rows, F, limit, alpha, shift);           \
+    if (vec) glu_clamped_vec_kernel<T><<<(int)blocks, 256, 0, stream>>>((const T*)gu, (T*)y, rows, F, limit, alpha, shift, cubic); \
+    else glu_clamped_kernel<T><<<(int)blocks, 256, 0, stream>>>((const T*)gu, (T*)y, rows, F, limit, alpha, shift, cubic);       \
   } while (0)
   if (dtype == DK_F32) LAUNCH(float);
   else if (dtype == DK_BF16) LAUNCH(__nv_bfloat16);
@@ -541,7 +557,7 @@ extern "C" int dk_router_topk(const float* logits, int ld, int* choice, float* w
 }
 
 // scored == 0: the softmax over the chosen logits.  scored == 1: sigmoid scores, `correction` [E] (or null) added for the choice
-// only, weights = chosen scores / their sum * route_scale.
+// only, weights = chosen scores / their sum * route_scale.  scored == 2: the same with weights = chosen scores * route_scale.
 extern "C" int dk_router(const void* x, const void* w, float* logits, int* choice, float* weight, int T_, int d, int n_rows, int E, int top,
                          const float* correction, float route_scale, int scored, int dtype, cudaStream_t stream) {
   if (T_ == 0) return 0;
@@ -641,4 +657,16 @@ extern "C" int dk_experts_combine(const float* z, const float* weight, int top, 
                                                                       (__nv_bfloat16*)out, d);
   else DK_REQUIRE(false, "experts_combine: unknown dtype %d", dtype);
   return dk_check_launch("experts_combine");
+}
+
+extern "C" int dk_experts_scale_rows(const void* x, const float* weight, void* xs, int T_, int top, int d, int dtype, cudaStream_t stream) {
+  if (T_ == 0) return 0;
+  DK_REQUIRE(T_ > 0 && top > 0 && top <= MAX_TOP && d > 0, "experts_scale_rows: bad sizes T=%d top=%d d=%d", T_, top, d);
+  const dim3 grid(T_, top);
+  const int threads = d >= 1024 ? 256 : 128;
+  if (dtype == DK_F32) experts_scale_rows_kernel<float><<<grid, threads, 0, stream>>>((const float*)x, weight, (float*)xs, d);
+  else if (dtype == DK_BF16)
+    experts_scale_rows_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((const __nv_bfloat16*)x, weight, (__nv_bfloat16*)xs, d);
+  else DK_REQUIRE(false, "experts_scale_rows: unknown dtype %d", dtype);
+  return dk_check_launch("experts_scale_rows");
 }

@@ -10,7 +10,9 @@
 //                        x <- x + vec            one vector for all tokens
 //                    then out = norm(x) * w with the layer norm without bias, (x - mean) / sqrt(var + eps), var the
 //                    mean of the squared deviations, or the RMS norm x / sqrt(mean(x^2) + eps); w == nullptr: out = x.
+//                    A bias b (or null) is added behind the weight.
 //                    All sums and statistics are 32 bit; only `out` is rounded to the compute type.
+//   sublayer_norm_add  x <- x + norm(y) * w + b: the norm sits on a sublayer's output.
 #include "common.cuh"
 
 namespace {
@@ -56,8 +58,8 @@ __global__ void remember_tokens_kernel(const int* __restrict__ tokens, const int
 // One block per output row r (token tk = rows ? rows[r] : r); the settled row is kept in shared memory between the passes.
 template <typename T, typename TO>
 __global__ void residual_norm_kernel(float* __restrict__ X, const T* __restrict__ y1, const T* __restrict__ y2, const float* __restrict__ e,
-                                     const float* __restrict__ vec, const float* __restrict__ w, TO* __restrict__ out,
-                                     const int* __restrict__ rows, int d, float eps, int kind, int write_back) {
+                                     const float* __restrict__ vec, const float* __restrict__ w, const float* __restrict__ b,
+                                     TO* __restrict__ out, const int* __restrict__ rows, int d, float eps, int kind, int write_back) {
   extern __shared__ __align__(16) float xs[];   // d floats + 33
   float* scratch = xs + d;
   const int r = blockIdx.x;
@@ -93,7 +95,38 @@ __global__ void residual_norm_kernel(float* __restrict__ X, const T* __restrict_
   }
   ss = block_sum(ss, scratch);
   const float inv = 1.f / sqrtf(ss / (float)d + eps);
-  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_f32<TO>((xs[i] - mean) * inv * w[i]);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_f32<TO>((xs[i] - mean) * inv * w[i] + (b != nullptr ? b[i] : 0.f));
+}
+
+// The step behind a sublayer whose OUTPUT is normed (the sublayer itself read the stream as it was):
+//     x <- x + norm(y) * w + b
+// with the layer norm or the RMS norm of the sublayer's output y over the width and a bias b (or null), all in 32 bit; `out` (or null) takes the new x rounded to the compute type, for the next sublayer to read.
+template <typename T, typename TO>
+__global__ void sublayer_norm_add_kernel(float* __restrict__ X, const T* __restrict__ y, const float* __restrict__ w,
+                                         const float* __restrict__ b, TO* __restrict__ out, int d, float eps, int kind) {
+  extern __shared__ __align__(16) float ys[];   // d floats + 34
+  float* scratch = ys + d;
+  const size_t at = (size_t)blockIdx.x * d;
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float v = to_f32<T>(y[at + i]);
+    ys[i] = v;
+    sum += v;
+  }
+  float mean = 0.f;
+  if (kind == 1) mean = block_sum(sum, scratch) / (float)d;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float c = ys[i] - mean;
+    ss += c * c;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.f / sqrtf(ss / (float)d + eps);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float v = X[at + i] + ((ys[i] - mean) * inv * w[i] + (b != nullptr ? b[i] : 0.f));
+    X[at + i] = v;
+    if (out != nullptr) out[at + i] = from_f32<TO>(v);
+  }
 }
 
 // out = factor * sum over the branches k of  rms_norm(y_k + b_k) * w_k : sublayers that run side by side, each normed over the
@@ -173,8 +206,8 @@ extern "C" int dk_remember_tokens(const int* tokens, const int* row_q_start, con
   return dk_check_launch("remember_tokens");
 }
 
-extern "C" int dk_residual_norm(float* X, const void* y1, const void* y2, const float* e, const float* vec, const float* w, void* out,
-                                const int* rows, int n_rows, int d, float eps, int kind, int write_back, int y_dtype, int out_dtype,
+extern "C" int dk_residual_norm(float* X, const void* y1, const void* y2, const float* e, const float* vec, const float* w, const float* b,
+                                void* out, const int* rows, int n_rows, int d, float eps, int kind, int write_back, int y_dtype, int out_dtype,
                                 cudaStream_t stream) {
   if (n_rows == 0) return 0;
   DK_REQUIRE(n_rows > 0 && d > 0, "residual_norm: bad sizes rows=%d d=%d", n_rows, d);
@@ -184,7 +217,7 @@ extern "C" int dk_residual_norm(float* X, const void* y1, const void* y2, const 
   const int threads = d >= 4096 ? 512 : (d >= 1024 ? 256 : 128);
   const size_t smem = (size_t)(d + 36) * sizeof(float);
 #define LAUNCH(T, TO)                                                                                                          \
-  residual_norm_kernel<T, TO><<<n_rows, threads, smem, stream>>>(X, (const T*)y1, (const T*)y2, e, vec, w, (TO*)out, rows, d, eps, \
+  residual_norm_kernel<T, TO><<<n_rows, threads, smem, stream>>>(X, (const T*)y1, (const T*)y2, e, vec, w, b, (TO*)out, rows, d, eps, \
                                                                  kind, write_back)
   if (y_dtype == DK_F32 && out_dtype == DK_F32) LAUNCH(float, float);
   else if (y_dtype == DK_BF16 && out_dtype == DK_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
@@ -193,4 +226,23 @@ extern "C" int dk_residual_norm(float* X, const void* y1, const void* y2, const 
   else DK_REQUIRE(false, "residual_norm: unsupported dtypes y=%d out=%d", y_dtype, out_dtype);
 #undef LAUNCH
   return dk_check_launch("residual_norm");
+}
+
+extern "C" int dk_sublayer_norm_add(float* X, const void* y, const float* w, const float* b, void* out, int T_, int d,
+                                    float eps, int kind, int y_dtype, int out_dtype, cudaStream_t stream) {
+  if (T_ == 0) return 0;
+  DK_REQUIRE(T_ > 0 && d > 0, "sublayer_norm_add: bad sizes T=%d d=%d", T_, d);
+  DK_REQUIRE(d <= 12000, "sublayer_norm_add: width %d is above the 12000 this kernel keeps in shared memory", d);
+  DK_REQUIRE(kind == 0 || kind == 1, "sublayer_norm_add: unknown norm kind %d", kind);
+  DK_REQUIRE(w != nullptr, "sublayer_norm_add: the norm has no weight");
+  const int threads = d >= 4096 ? 512 : (d >= 1024 ? 256 : 128);
+  const size_t smem = (size_t)(d + 36) * sizeof(float);
+#define LAUNCH(T, TO) sublayer_norm_add_kernel<T, TO><<<T_, threads, smem, stream>>>(X, (const T*)y, w, b, (TO*)out, d, eps, kind)
+  if (y_dtype == DK_F32 && out_dtype == DK_F32) LAUNCH(float, float);
+  else if (y_dtype == DK_BF16 && out_dtype == DK_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else if (y_dtype == DK_BF16 && out_dtype == DK_F32) LAUNCH(__nv_bfloat16, float);
+  else if (y_dtype == DK_F32 && out_dtype == DK_BF16) LAUNCH(float, __nv_bfloat16);
+  else DK_REQUIRE(false, "sublayer_norm_add: unsupported dtypes y=%d out=%d", y_dtype, out_dtype);
+#undef LAUNCH
+  return dk_check_launch("sublayer_norm_add");
 }

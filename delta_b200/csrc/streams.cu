@@ -207,9 +207,12 @@ __global__ void activation_kernel(const T* __restrict__ in, T* __restrict__ out,
   }
 }
 
-__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
-    x[i] = cap * tanhf(x[i] / cap);
+// x <- x * scale, then x <- cap * tanh(x / cap) (cap <= 0: no cap)
+__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap, float scale) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const float v = x[i] * scale;
+    x[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
+  }
 }
 
 int grid_for(size_t n, int threads) {
@@ -277,9 +280,9 @@ extern "C" int dk_activation(const void* in, void* out, long long n, int kind, i
   return dk_check_launch("activation");
 }
 
-extern "C" int dk_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+extern "C" int dk_softcap(float* x, long long n, float cap, float scale, cudaStream_t stream) {
   if (n == 0) return 0;
-  DK_REQUIRE(n > 0 && cap > 0.f, "softcap: bad arguments n=%lld cap=%g", n, cap);
-  softcap_kernel<<<grid_for((size_t)n, 256), 256, 0, stream>>>(x, (size_t)n, cap);
+  DK_REQUIRE(n > 0 && (cap > 0.f || scale != 1.f), "softcap: bad arguments n=%lld cap=%g scale=%g", n, cap, scale);
+  softcap_kernel<<<grid_for((size_t)n, 256), 256, 0, stream>>>(x, (size_t)n, cap, scale);
   return dk_check_launch("softcap");
 }

@@ -40,10 +40,10 @@ class RowAttnParams(C.Structure):
     """Mirror of ``DkRowAttnParams`` in csrc/row_attention_params.h."""
     _fields_ = [
         ("q", P), ("out", P), ("cache", P), ("block_table", P), ("tok_row", P), ("tok_pos", P), ("row_q_start", P),
-        ("row_q_len", P), ("row_pos_start", P), ("sink", P), ("scratch", P), ("err", P),
+        ("row_q_len", P), ("row_pos_start", P), ("sink", P), ("dist_bias", P), ("scratch", P), ("err", P),
         ("T", I), ("rows", I), ("H", I), ("KV", I), ("dk", I), ("dv", I), ("ps", I), ("max_pages", I), ("num_pages", I),
         ("q_stride", I), ("q_head_stride", I), ("row_width", I), ("k_off", I), ("v_off", I), ("window", I), ("dtype", I),
-        ("splits", I), ("row_filter", I), ("scale", F), ("reserved", I),
+        ("splits", I), ("row_filter", I), ("scale", F), ("softcap", F), ("dist_max", I), ("reserved", I),
     ]
 
 
@@ -53,17 +53,18 @@ _SIGNATURES = {
     "dk_embedding_streams": [P, P, P, I, I, I, I, I, P, P],
     "dk_stream_norm": [P, P, P, P, P, P, P, P, I, I, I, F, I, I, I, P],
     "dk_activation": [P, P, L, I, I, P],
-    "dk_softcap": [P, L, F, P],
+    "dk_softcap": [P, L, F, F, P],
     "dk_conv_silu": [P, I, P, P, P, P, P, P, P, P, I, I, I, I, P, I, I, P],
     "dk_selective_scan": [P, P, P, I, I, I, P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P, P, P],
     "dk_attention_rows_plain": [C.POINTER(RowAttnParams), P],
     "dk_rows_append": [P, I, P, P, P, I, P, I, P, I, I, I, I, I, I, I, I, I, I, I, I, I, P, P],
-    "dk_latent_prepare": [P, I, P, P, P, I, P, I, P, I, I, I, P, F, P, I, I, I, I, I, I, I, P, P],
+    "dk_latent_prepare": [P, I, P, P, P, I, P, I, P, I, I, I, P, F, P, I, I, I, I, I, I, P, I, I, P, P],
     "dk_attention_rows_mma_supported": [C.POINTER(RowAttnParams)],
     "dk_attention_rows_mma": [C.POINTER(RowAttnParams), I, I, P, P],
     "dk_gemm_nt_plain_batched": [P, P, P, I, I, I, I, I, I, I, L, L, L, I, I, P],
     "dk_embedding": [P, P, P, I, I, I, I, P, P],
     "dk_rms_norm": [P, P, P, P, P, I, I, F, I, I, I, P],
+    "dk_rms_norm_strided": [P, I, P, P, I, I, F, I, I, P],
     "dk_silu_mul": [P, P, I, I, I, P],
     "dk_rope_append": [P, P, P, P, I, P, I, P, I, I, I, I, I, I, I, I, P, P],
     "dk_gemm_nt_plain": [P, P, P, I, I, I, I, I, I, I, I, P],
@@ -90,8 +91,9 @@ _SIGNATURES = {
     "dk_wait_check": [P, C.c_longlong, P],
     "dk_embedding_pair": [P, P, P, P, P, P, P, F, P, L, L, L, P, P, I, I, I, I, P, P],
     "dk_remember_tokens": [P, P, P, P, P, I, P],
-    "dk_residual_norm": [P, P, P, P, P, P, P, P, I, I, F, I, I, I, I, P],
-    "dk_rows_append_unit": [P, I, P, P, P, I, P, I, P, I, I, I, I, I, I, I, I, I, I, I, I, I, F, I, P, P, P, F, I, P, P],
+    "dk_residual_norm": [P, P, P, P, P, P, P, P, P, I, I, F, I, I, I, I, P],
+    "dk_sublayer_norm_add": [P, P, P, P, P, I, I, F, I, I, I, P],
+    "dk_rows_append_unit": [P, I, P, P, P, I, P, I, P, I, I, I, I, I, I, I, I, I, I, I, I, I, F, I, P, P, P, F, I, F, I, I, P, P],
     "dk_decay_attention_slice": [I, I, I, I],
     "dk_decay_attention": [P, I, I, I, I, I, P, P, P, P, P, P, I, I, I, I, I, I, P],
     "dk_decay_attention_chunk": [],
@@ -111,7 +113,7 @@ _SIGNATURES = {
     "dk_matrix_memory_chunked_supported": [I, I],
     "dk_matrix_memory_chunked": [P, I, I, I, I, F, P, P, F, F, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
     "dk_gated_rms_norm": [P, P, I, P, P, I, I, F, I, I, P],
-    "dk_glu_clamped": [P, P, L, I, F, F, F, I, P],
+    "dk_glu_clamped": [P, P, L, I, F, F, F, F, I, P],
     "dk_router_topk": [P, I, P, P, I, I, I, P],
     "dk_router": [P, P, P, P, P, I, I, I, I, I, P, F, I, I, P],
     "dk_experts_align": [P, I, I, P, I, P, I, I, P],
@@ -121,6 +123,7 @@ _SIGNATURES = {
     "dk_experts_gemm": [P, P, P, P, P, I, I, I, I, I, F, F, F, I, P],
     "dk_experts_combine": [P, P, I, P, P, I, P, I, I, I, P],
     "dk_experts_tile_rows": [],
+    "dk_experts_scale_rows": [P, P, P, I, I, I, I, P],
 }
 
 

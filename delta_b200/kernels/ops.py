@@ -126,6 +126,17 @@ def rms_norm(x, weight, eps, out, add=None, rows=None, cast_first=False):
     return out
 
 
+def rms_norm_strided(x, ld, weight, eps, out):
+    """out[r] = rmsnorm(x[r, :d]) * weight for rows of ``x`` that lie ``ld`` elements apart, d = out.shape[1] (the first columns of
+    a wider product's result); statistics and weight in 32 bit, rounded once."""
+    n, d = out.shape
+    if x.shape[0] != n or ld < d or x.numel() < (n - 1) * ld + d:
+        raise KernelError(f"rms_norm_strided: {n} rows of {d} columns, {ld} apart, do not lie in a tensor of shape {tuple(x.shape)}")
+    _l.check(_l.load().dk_rms_norm_strided(_ptr(x, "x"), int(ld), _ptr(weight, "weight"), _ptr(out, "out", x.dtype), n, d, float(eps),
+                                           dtype_code(x.dtype), dtype_code(weight.dtype), _stream()), "rms_norm_strided")
+    return out
+
+
 def silu_mul(gate_up, out):
     T, I2 = gate_up.shape
     _l.check(_l.load().dk_silu_mul(_ptr(gate_up, "gate_up"), _ptr(out, "out", gate_up.dtype), T, I2 // 2,
@@ -461,9 +472,9 @@ def activation(x, out, kind: str):
     return out
 
 
-def softcap(logits, cap: float):
-    """logits <- cap * tanh(logits / cap), in place (float32)."""
-    _l.check(_l.load().dk_softcap(_ptr(logits, "logits", torch.float32), logits.numel(), float(cap), _stream()), "softcap")
+def softcap(logits, cap: Optional[float], scale: float = 1.0):
+    """logits <- logits * scale, then logits <- cap * tanh(logits / cap) (``cap`` None: no cap), in place (float32)."""
+    _l.check(_l.load().dk_softcap(_ptr(logits, "logits", torch.float32), logits.numel(), float(cap or 0.0), float(scale), _stream()), "softcap")
     return logits
 
 
@@ -511,7 +522,10 @@ RowAttnParams = _l.RowAttnParams
 
 
 def row_attn_params(*, q, q_stride, q_head_stride, out, cache, block_table, tok_row, tok_pos, row_q_start, row_q_len,
-                    row_pos_start, H, KV, dk, dv, ps, row_width, k_off, v_off, scale, window=0, sink=None, err=None) -> RowAttnParams:
+                    row_pos_start, H, KV, dk, dv, ps, row_width, k_off, v_off, scale, window=0, sink=None, softcap=None, dist_bias=None,
+                    err=None) -> RowAttnParams:
+    """``softcap`` c: the scaled score s becomes c tanh(s / c).  ``dist_bias`` float32 [D + 1, H]: row min(i - j, D) is added to the
+    scores of query i and key j, one column a head (after the cap; the scale does not multiply it)."""
     i32 = torch.int32
     if tuple(cache.shape[1:]) != (KV, ps, row_width) or cache.dtype != q.dtype:
         raise KernelError(f"attention_rows: cache has shape {tuple(cache.shape)} / {cache.dtype}, expected [pages, {KV}, {ps}, {row_width}] of {q.dtype}")
@@ -522,6 +536,11 @@ def row_attn_params(*, q, q_stride, q_head_stride, out, cache, block_table, tok_
     p.row_q_start, p.row_q_len = _ptr(row_q_start, "row_q_start", i32), _ptr(row_q_len, "row_q_len", i32)
     p.row_pos_start = _ptr(row_pos_start, "row_pos_start", i32)
     p.sink = _ptr(sink, "sink", torch.float32)
+    if dist_bias is not None:
+        if dist_bias.dim() != 2 or dist_bias.shape[1] != H or dist_bias.shape[0] < 1:
+            raise KernelError(f"attention_rows: the distance biases have shape {tuple(dist_bias.shape)}, expected [distances, {H}]")
+        p.dist_bias, p.dist_max = _ptr(dist_bias, "dist_bias", torch.float32), dist_bias.shape[0] - 1
+    p.softcap = float(softcap or 0.0)
     p.err = _ptr(err, "err", i32)
     p.T, p.rows = tok_row.shape[0], block_table.shape[0]
     p.H, p.KV, p.dk, p.dv, p.ps = H, KV, dk, dv, ps
@@ -558,13 +577,16 @@ def rows_append(src, tok_pos, tok_row, block_table, cache, *, H, KV, dk, dv, ps,
 
 
 def latent_prepare(src, tok_pos, tok_row, block_table, cache, qabs, *, norm_weight, eps, H, dq, dr, R, ps, table=None, rot_dims=0,
-                   interleaved=True, err=None):
+                   interleaved=True, low=None, low_offset=0, err=None):
     """``src`` [T, H*(dq+dr) + R + dr]: per head the plain and the rotated query part, then the latent and the shared
-    rotated key part.  Writes the normalised latent and the rotated key part to the token's row of ``cache``
+    rotated key part; with ``low`` [T, >= low_offset + R + dr] the latent and the key part are read from its columns from
+    ``low_offset`` on and ``src`` [T, H*(dq+dr)] holds the queries only.  Writes the normalised latent and the rotated key part to the token's row of ``cache``
     [pages, 1, ps, R+dr] and the heads' rotated query parts to ``qabs`` [T, H, R+dr] at [R, R+dr)."""
     T = src.shape[0]
     if cache is not None and (tuple(cache.shape[1:]) != (1, ps, R + dr) or cache.dtype != src.dtype):
         raise KernelError(f"latent_prepare: cache has shape {tuple(cache.shape)} / {cache.dtype}, expected [pages, 1, {ps}, {R + dr}] of {src.dtype}")
+    if low is not None and (low.shape[0] != T or low.shape[1] - int(low_offset) < R + dr):
+        raise KernelError(f"latent_prepare: rows of {low.shape[1]} entries do not hold the latent from column {low_offset} on")
     if tuple(qabs.shape) != (T, H, R + dr):
         raise KernelError(f"latent_prepare: qabs has shape {tuple(qabs.shape)}, expected {(T, H, R + dr)}")
     i32 = torch.int32
@@ -573,7 +595,9 @@ def latent_prepare(src, tok_pos, tok_row, block_table, cache, qabs, *, norm_weig
         _ptr(block_table, "block_table", i32), block_table.shape[1] if block_table is not None else 0, _ptr(cache, "cache"),
         cache.shape[0] if cache is not None else 0, _ptr(table, "table", torch.float32), table.shape[0] if table is not None else 0,
         int(rot_dims), int(bool(interleaved)), _ptr(norm_weight, "norm_weight", torch.float32), float(eps),
-        _ptr(qabs, "qabs", src.dtype), T, H, dq, dr, R, ps, dtype_code(src.dtype), _ptr(err, "err", i32), _stream()), "latent_prepare")
+        _ptr(qabs, "qabs", src.dtype), T, H, dq, dr, R, ps,
+        (_ptr(low, "low", src.dtype) + int(low_offset) * low.element_size()) if low is not None else None,
+        low.shape[1] if low is not None else 0, dtype_code(src.dtype), _ptr(err, "err", i32), _stream()), "latent_prepare")
 
 
 def gemm_nt_plain_batched(a_ptr, w_ptr, c_ptr, M, N, K, lda, ldw, ldc, batch, sa, sw, sc, in_dtype, out_dtype):
@@ -601,12 +625,14 @@ def attention_rows_mma(params: RowAttnParams, max_m: int, splits: int = 1, scrat
 
 def rows_append_unit(src, tok_pos, tok_row, block_table, cache, *, H, KV, dk, dv, ps, row_width, k_off, v_off, table=None,
                      rot_dims=0, interleaved=True, unit_eps=None, value_from_key=False, bias=None, q_norm=None, k_norm=None,
-                     pre_eps=0.0, err=None):
+                     pre_eps=0.0, norm_whole=False, q_temp=None, err=None):
     """As ``rows_append``, one warp per head in 32 bit: after the rotation every query and key head is divided by its root
     mean square, sqrt(mean(x^2) + ``unit_eps``) (None: not), and rounded once.  ``value_from_key``: ``src`` holds no v;
     the value is the key as it was projected, before rotation and norm.  ``bias`` (float32, one entry per column of q, k
     and v) is added as the heads are read; ``q_norm`` / ``k_norm`` (float32 [dk]): the RMS norm with this weight and
-    ``pre_eps`` on every query / key head before the rotation."""
+    ``pre_eps`` on every query / key head before the rotation; ``norm_whole``: one norm over all of q's columns and one over
+    all of k's, with weights [H*dk] and [KV*dk].  ``q_temp`` (coef, every): the query at position p is multiplied by
+    1 + coef * ln(floor((p + 1) / every) + 1).  ``KV`` 0 with no cache: ``src`` holds queries only."""
     T = src.shape[0]
     if cache is not None and (tuple(cache.shape[1:]) != (KV, ps, row_width) or cache.dtype != src.dtype):
         raise KernelError(f"rows_append_unit: cache has shape {tuple(cache.shape)} / {cache.dtype}, expected [pages, {KV}, {ps}, {row_width}] of {src.dtype}")
@@ -619,7 +645,8 @@ def rows_append_unit(src, tok_pos, tok_row, block_table, cache, *, H, KV, dk, dv
         cache.shape[0] if cache is not None else 0, _ptr(table, "table", torch.float32), table.shape[0] if table is not None else 0,
         int(rot_dims), int(bool(interleaved)), T, H, KV, dk, dv, ps, row_width, k_off, v_off, int(unit_eps is not None),
         float(unit_eps or 0.0), int(bool(value_from_key)), _ptr(bias, "bias", torch.float32), _ptr(q_norm, "q_norm", torch.float32),
-        _ptr(k_norm, "k_norm", torch.float32), float(pre_eps), dtype_code(src.dtype), _ptr(err, "err", i32), _stream()), "rows_append_unit")
+        _ptr(k_norm, "k_norm", torch.float32), float(pre_eps), int(bool(norm_whole)), float(q_temp[0]) if q_temp else 0.0,
+        int(q_temp[1]) if q_temp else 0, dtype_code(src.dtype), _ptr(err, "err", i32), _stream()), "rows_append_unit")
 
 
 # ---- a residual stream of one 32-bit copy whose sublayers run side by side ---------------------------------------
@@ -650,11 +677,12 @@ def remember_tokens(tokens, prev_state, *, row_q_start, row_q_len, row_slot):
              "remember_tokens")
 
 
-def residual_norm(X, out, *, updates=(), extra=None, vec=None, weight=None, eps=0.0, kind="layer", rows=None, write_back=True):
+def residual_norm(X, out, *, updates=(), extra=None, vec=None, weight=None, bias=None, eps=0.0, kind="layer", rows=None, write_back=True):
     """The step between two layers on a 32-bit stream X [T, d]:  X <- X + (y1 + y2) (``updates``: none, one or two tensors
     of the compute type), X <- X + ``extra`` (float32 [T, d]), X <- X + ``vec`` (float32 [d]), stored when ``write_back``;
     then ``out`` = norm(X) * weight with the layer norm without bias or the RMS norm (``weight`` None: X itself).
-    ``rows``: only these tokens, in this order.  ``out`` None: only the sums are done."""
+    ``bias`` (float32 [d]) is added behind the weight.  ``rows``: only these tokens, in this order.  ``out`` None: only the sums
+    are done."""
     T, d = X.shape
     n = rows.shape[0] if rows is not None else T
     if len(updates) > 2:
@@ -670,8 +698,23 @@ def residual_norm(X, out, *, updates=(), extra=None, vec=None, weight=None, eps=
     ydt = dtype_code(y1.dtype) if y1 is not None else (dtype_code(out.dtype) if out is not None and out.dtype != f32 else F32)
     _l.check(_l.load().dk_residual_norm(
         _ptr(X, "X", f32), _ptr(y1, "update"), _ptr(y2, "update", y1.dtype if y1 is not None else None), _ptr(extra, "extra", f32),
-        _ptr(vec, "vec", f32), _ptr(weight, "weight", f32), _ptr(out, "out"), _ptr(rows, "rows", torch.int32), n, d, float(eps),
+        _ptr(vec, "vec", f32), _ptr(weight, "weight", f32), _ptr(bias, "bias", f32) if weight is not None else None, _ptr(out, "out"),
+        _ptr(rows, "rows", torch.int32), n, d, float(eps),
         NORM_KINDS[kind], int(bool(write_back)), ydt, dtype_code(out.dtype) if out is not None else F32, _stream()), "residual_norm")
+    return out
+
+
+def sublayer_norm_add(X, y, out, *, weight, bias=None, eps=0.0, kind="layer"):
+    """X <- X + norm(y) * weight + bias on a 32-bit stream X [T, d], with the norm of the sublayer's output y (compute type or
+    float32) over the width; ``bias`` (float32 [d]) may be absent.  ``out`` (or None) takes the new X rounded to its type."""
+    T, d = X.shape
+    if tuple(y.shape) != (T, d) or (out is not None and tuple(out.shape) != (T, d)):
+        raise KernelError(f"sublayer_norm_add: the stream is {(T, d)}, the sublayer's output {tuple(y.shape)}")
+    f32 = torch.float32
+    _l.check(_l.load().dk_sublayer_norm_add(
+        _ptr(X, "X", f32), _ptr(y, "y"), _ptr(weight, "weight", f32), _ptr(bias, "bias", f32), _ptr(out, "out"),
+        T, d, float(eps), NORM_KINDS[kind], dtype_code(y.dtype), dtype_code(out.dtype) if out is not None else F32, _stream()),
+        "sublayer_norm_add")
     return out
 
 
@@ -900,12 +943,12 @@ def matrix_memory_chunked(src, q_off, k_off, v_off, q_scale, gates, gate_bias, c
 
 # ---- gated feed-forwards and a mixture of experts ---------------------------------------------------------------
 
-def glu_clamped(gate_up, out, limit=-1.0, alpha=1.702, shift=1.0):
-    """out = g' * sigmoid(alpha g') * (u' + shift) from rows [g | u], g' = min(g, limit), u' = clamp(u, -limit, limit)
+def glu_clamped(gate_up, out, limit=-1.0, alpha=1.702, shift=1.0, cubic=0.0):
+    """out = g' * sigmoid(alpha (g' + cubic g'^3)) * (u' + shift) from rows [g | u], g' = min(g, limit), u' = clamp(u, -limit, limit)
     (``limit`` negative: unclamped)."""
     rows, F2 = gate_up.shape
     _l.check(_l.load().dk_glu_clamped(_ptr(gate_up, "gate_up"), _ptr(out, "out", gate_up.dtype), rows, F2 // 2, float(limit), float(alpha),
-                                      float(shift), dtype_code(gate_up.dtype), _stream()), "glu_clamped")
+                                      float(shift), float(cubic), dtype_code(gate_up.dtype), _stream()), "glu_clamped")
     return out
 
 
@@ -916,16 +959,18 @@ def router_topk(logits, experts, top, choice, weight):
                                       _ptr(weight, "weight", torch.float32), T, int(experts), int(top), _stream()), "router_topk")
 
 
-def router(x, w, experts, top, logits, choice, weight, scoring="softmax", correction=None, scale=1.0):
+def router(x, w, experts, top, logits, choice, weight, scoring="softmax", correction=None, scale=1.0, normalize=True):
     """logits = x w^T in 32 bit ([T, rows of w]; the first ``experts`` rows are the experts'), and per token the ``top`` largest of
     the experts' logits with the softmax over them.  ``scoring`` "sigmoid": scores s = sigmoid(logit); the ``top`` largest of
-    s + ``correction`` (float32 [experts] or None) are chosen; the weights are the chosen s divided by their sum, times ``scale``."""
+    s + ``correction`` (float32 [experts] or None) are chosen; the weights are the chosen s divided by their sum (``normalize``
+    False: the chosen s themselves), times ``scale``."""
     T, d = x.shape
     if scoring not in ("softmax", "sigmoid"):
         raise KernelError(f"router: unknown scoring '{scoring}'")
     _l.check(_l.load().dk_router(_ptr(x, "x"), _ptr(w, "w", x.dtype), _ptr(logits, "logits", torch.float32), _ptr(choice, "choice", torch.int32),
                                  _ptr(weight, "weight", torch.float32), T, d, w.shape[0], int(experts), int(top),
-                                 _ptr(correction, "correction", torch.float32), float(scale), int(scoring == "sigmoid"),
+                                 _ptr(correction, "correction", torch.float32), float(scale),
+                                 (1 if normalize else 2) if scoring == "sigmoid" else 0,
                                  dtype_code(x.dtype), _stream()), "router")
 
 
@@ -980,10 +1025,23 @@ def experts_gemm(a, w, out, sorted_slots, tile_expert, *, top, n, k, act=False, 
                                        code, float(limit), float(alpha), float(shift), dtype_code(a.dtype), _stream()), "experts_gemm")
 
 
-def experts_combine(z, weight, out, shared=None, gate_logit=None, gate_stride=0):
-    """out[t] = sum_j weight[t, j] z[t*top + j] (+ sigmoid(gate logit of t) * shared[t]); ``gate_logit``: an address (float32)."""
+def experts_scale_rows(x, weight, out):
+    """out[t * top + j] = weight[t, j] * x[t], rounded once to the type of x."""
+    T, d = x.shape
+    top = weight.shape[1]
+    if tuple(out.shape) != (T * top, d) or weight.shape[0] != T:
+        raise KernelError(f"experts_scale_rows: {T} tokens with {top} weights each do not give rows of shape {tuple(out.shape)}")
+    _l.check(_l.load().dk_experts_scale_rows(_ptr(x, "x"), _ptr(weight, "weight", torch.float32), _ptr(out, "out", x.dtype), T, top, d,
+                                             dtype_code(x.dtype), _stream()), "experts_scale_rows")
+    return out
+
+
+def experts_combine(z, weight, out, shared=None, gate_logit=None, gate_stride=0, top=None):
+    """out[t] = sum_j weight[t, j] z[t*top + j] (+ sigmoid(gate logit of t) * shared[t]; no gate logit: + shared[t]); ``gate_logit``: an
+    address (float32).  ``weight`` None with ``top``: every weight is 1."""
     T, d = out.shape
-    _l.check(_l.load().dk_experts_combine(_ptr(z, "z", torch.float32), _ptr(weight, "weight", torch.float32), weight.shape[1],
+    _l.check(_l.load().dk_experts_combine(_ptr(z, "z", torch.float32), _ptr(weight, "weight", torch.float32),
+                                          weight.shape[1] if weight is not None else int(top),
                                           _ptr(shared, "shared", out.dtype), gate_logit, int(gate_stride), _ptr(out, "out"), T, d,
                                           dtype_code(out.dtype), _stream()), "experts_combine")
     return out

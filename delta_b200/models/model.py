@@ -127,6 +127,6 @@ class Model:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=ctx.device)
         h = self.stream.finish(ctx, x, pending, self.final_norm, ctx.logit_rows)
         logits = linear.linear(ctx, h, self.lm_head, out_dtype=torch.float32)
-        if self.spec.logit_softcap:
-            ops.softcap(logits, self.spec.logit_softcap)
+        if self.spec.logit_softcap or self.spec.logit_scale != 1.0:
+            ops.softcap(logits, self.spec.logit_softcap, self.spec.logit_scale)
         return logits

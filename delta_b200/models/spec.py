@@ -43,6 +43,7 @@ class ModelSpec:
     max_positions: int = 0
     stream: Optional[PartSpec] = None       # the residual stream (None: one copy in the compute type)
     logit_softcap: Optional[float] = None   # logits <- cap * tanh(logits / cap)
+    logit_scale: float = 1.0                # logits <- logits * scale (before the cap)
     ignorable_tensors: tuple = ()   # shell patterns of tensor names a model folder may hold beside the ones asked for
 
     def __post_init__(self):

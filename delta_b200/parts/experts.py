@@ -13,7 +13,10 @@ the shared expert's gate row are one matrix, so one product gives both.
 
 Options: ``scoring`` "sigmoid": scores s = sigmoid(z); the ``top`` largest of s + correction (a tensor ``correction`` [E] when
 ``correction`` is set) are chosen, and the weights are the chosen s (without the correction) divided by their sum (+ 1e-20), times
-``route_scale``.  ``activation`` "relu_squared": an expert is  W_down relu(W_up h)^2  with no gate branch.  ``wide_output``: the
+``route_scale``; ``normalize`` False: the chosen s themselves, times ``route_scale``.  ``weight_input``: a choice's weight multiplies
+what its expert reads, out = sum expert(weight * h), not what it gives (the rows weight * h are made first, rounded once to the
+compute type).  ``shared`` {intermediate, limit, alpha, shift, gate}: ``gate`` False leaves the shared expert's sigmoid gate (and the
+tensor ``shared.sg``) out, so it is added as it is.  ``activation`` "relu_squared": an expert is  W_down relu(W_up h)^2  with no gate branch.  ``wide_output``: the
 weighted sum is handed on in 32 bit (for a 32-bit residual stream), not rounded to the compute type.
 """
 from __future__ import annotations
@@ -38,7 +41,8 @@ class Experts(FeedForward):
 
     def __init__(self, prefix: str, width: int, experts: int, top: int, intermediate: int, limit=None, alpha: float = 1.702,
                  shift: float = 1.0, shared: Optional[dict] = None, scoring: str = "softmax", correction: bool = False,
-                 route_scale: float = 1.0, activation: str = "clamped_glu", wide_output: bool = False):
+                 route_scale: float = 1.0, activation: str = "clamped_glu", wide_output: bool = False, normalize: bool = True,
+                 weight_input: bool = False):
         self.prefix, self.width = prefix, int(width)
         self.experts, self.top, self.intermediate = int(experts), int(top), int(intermediate)
         if not (1 <= self.top <= self.experts):
@@ -57,8 +61,12 @@ class Experts(FeedForward):
         self.wide_output = bool(wide_output)
         if self.wide_output and shared:
             raise ValueError("the 32-bit output is for experts without a shared expert (whose output has the compute type)")
+        self.normalize, self.weight_input = bool(normalize), bool(weight_input)
+        if not self.normalize and scoring != "sigmoid":
+            raise ValueError("weights that are not normalised belong to sigmoid scores")
         self.correction = None
         self.shared = None
+        self.shared_gate = bool(shared.get("gate", True)) if shared else False
         if shared:
             self.shared = ClampedGLU(prefix + "shared.", width, int(shared["intermediate"]), limit=shared.get("limit"),
                                      alpha=shared.get("alpha", alpha), shift=shared.get("shift", shift))
@@ -73,12 +81,12 @@ class Experts(FeedForward):
             specs += ([TensorSpec(f"{p}e{e}.gate", (F, d))] if self.gated else []) + [TensorSpec(f"{p}e{e}.up", (F, d)),
                                                                                      TensorSpec(f"{p}e{e}.down", (d, F))]
         if self.shared is not None:
-            specs += self.shared.tensor_specs() + [TensorSpec(p + "shared.sg", (1, d))]
+            specs += self.shared.tensor_specs() + ([TensorSpec(p + "shared.sg", (1, d))] if self.shared_gate else [])
         return specs
 
     def bind(self, tensors):
         p = self.prefix
-        rows = [tensors[p + "router"]] + ([tensors[p + "shared.sg"]] if self.shared is not None else [])
+        rows = [tensors[p + "router"]] + ([tensors[p + "shared.sg"]] if self.shared_gate else [])
         self.w_router = torch.cat(rows, dim=0).contiguous()
         if self.gated:
             self.w1 = torch.stack([torch.cat([tensors[f"{p}e{e}.gate"], tensors[f"{p}e{e}.up"]], dim=0) for e in range(self.experts)]).contiguous()
@@ -95,9 +103,14 @@ class Experts(FeedForward):
         z = torch.empty((T, self.w_router.shape[0]), dtype=f32, device=dev)        # [T, E (+1)]
         choice = torch.empty((T, top), dtype=i32, device=dev)
         weight = torch.empty((T, top), dtype=f32, device=dev)
-        ops.router(x, self.w_router, E, top, z, choice, weight, scoring=self.scoring, correction=self.correction, scale=self.route_scale)
+        ops.router(x, self.w_router, E, top, z, choice, weight, scoring=self.scoring, correction=self.correction, scale=self.route_scale,
+                   normalize=self.normalize)
         act = "gated" if self.gated else "relu_squared"
         slots = T * top
+        tokens = x
+        if self.weight_input:      # every slot reads a row of its own, weight * h; from here on a "token" is a slot
+            x = ops.experts_scale_rows(x, weight, torch.empty((slots, d), dtype=x.dtype, device=dev))
+            weight, top = None, 1
         # many rows an expert (prompt portions): tiles of 128 rows through the tcgen05 product; else tiles of 64 through warp-level MMA
         many = (x.dtype == torch.bfloat16 and "products" not in ctx.plain_kernels and slots >= TC_ROWS_PER_EXPERT * E and
                 ops.experts_gemm_tc_supported(F, d, self.gated) and ops.experts_gemm_tc_supported(d, F, False))
@@ -118,9 +131,11 @@ class Experts(FeedForward):
                              shift=self.shift)
             ops.experts_gemm(y, self.w2, out_slots, sorted_slots, tile_expert, top=top, n=d, k=F)
         out = torch.empty((T, d), dtype=f32 if self.wide_output else x.dtype, device=dev)     # wide: the weighted sum unrounded
+        top = self.top
         if self.shared is not None:
-            s = self.shared.forward(ctx, x)
-            ops.experts_combine(out_slots, weight, out, shared=s, gate_logit=z.data_ptr() + E * 4, gate_stride=z.shape[1])
+            s = self.shared.forward(ctx, tokens)
+            ops.experts_combine(out_slots, weight, out, shared=s, gate_logit=(z.data_ptr() + E * 4) if self.shared_gate else None,
+                                gate_stride=z.shape[1], top=top)
         else:
-            ops.experts_combine(out_slots, weight, out)
+            ops.experts_combine(out_slots, weight, out, top=top)
         return out

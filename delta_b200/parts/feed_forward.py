@@ -3,11 +3,18 @@
 activations, and a gated one with clamped branches."""
 from __future__ import annotations
 
+import math
+
 import torch
 
 from ..kernels import ops
 from . import linear
 from .base import FEED_FORWARDS, FeedForward, TensorSpec
+
+
+# g sigmoid(alpha (g + cubic g^3)) (u + shift): the constants of two common gates
+SILU_GATE = dict(alpha=1.0, shift=0.0, cubic=0.0)                                        # silu(g) u
+GELU_TANH_GATE = dict(alpha=2.0 * math.sqrt(2.0 / math.pi), shift=0.0, cubic=0.044715)   # 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) u
 
 
 @FEED_FORWARDS.register("swiglu")
@@ -70,14 +77,16 @@ class DenseMLP(FeedForward):
 
 @FEED_FORWARDS.register("clamped_glu")
 class ClampedGLU(FeedForward):
-    """down( g' * sigmoid(alpha g') * (u' + shift) ) with g' = min(gate x, limit) and u' = clamp(up x, -limit, limit)
-    (``limit`` None: unclamped).  Tensor names: ``<prefix>gate``, ``<prefix>up`` [I, d] and ``<prefix>down`` [d, I]."""
+    """down( g' * sigmoid(alpha (g' + cubic g'^3)) * (u' + shift) ) with g' = min(gate x, limit) and u' = clamp(up x, -limit, limit)
+    (``limit`` None: unclamped).  ``SILU_GATE`` and ``GELU_TANH_GATE`` are the constants of silu(g) u and of the tanh form of gelu,
+    gelu(g) u.  Tensor names: ``<prefix>gate``, ``<prefix>up`` [I, d] and ``<prefix>down`` [d, I]."""
 
-    def __init__(self, prefix: str, width: int, intermediate: int, limit=None, alpha: float = 1.702, shift: float = 1.0):
+    def __init__(self, prefix: str, width: int, intermediate: int, limit=None, alpha: float = 1.702, shift: float = 1.0,
+                 cubic: float = 0.0):
         self.prefix, self.width, self.intermediate = prefix, int(width), int(intermediate)
         if limit is not None and float(limit) < 0:
             raise ValueError(f"a clamp at {limit} is no limit")
-        self.limit, self.alpha, self.shift = (-1.0 if limit is None else float(limit)), float(alpha), float(shift)
+        self.limit, self.alpha, self.shift, self.cubic = (-1.0 if limit is None else float(limit)), float(alpha), float(shift), float(cubic)
         self.w_gate_up = self.w_down = None
 
     def tensor_specs(self):
@@ -92,5 +101,5 @@ class ClampedGLU(FeedForward):
     def forward(self, ctx, x):
         gu = linear.linear(ctx, x, self.w_gate_up)
         act = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
-        ops.glu_clamped(gu, act, self.limit, self.alpha, self.shift)
+        ops.glu_clamped(gu, act, self.limit, self.alpha, self.shift, self.cubic)
         return linear.linear(ctx, act, self.w_down)

@@ -9,6 +9,8 @@ value size ``value_dim``, latent size R):
     r            rotated by its position            the shared key part, cached
     k_h^plain    = U_h^K c ,   v_h = U_h^V c
     s_h(i, j)    = (q_h^plain(i) . k_h^plain(j) + rot(q_h^rot(i)) . r(j)) * scale ,  causal softmax over j <= i
+With ``q_rank`` Rq the queries go through a latent of their own, c_q = rmsnorm(W_dq h) * w_q, q = W_uq c_q (tensors ``dq``, ``dq.norm``,
+``uq`` instead of ``q``): W_dq rides with W_dkv in the first product, and a second product makes the heads' queries.
 The keys are never made: since q^plain . (U^K c) = ((U^K)^T q^plain) . c, the query is carried into the latent
 space once per new token (one product per head), attention then runs with one shared key-value head whose key is the
 cached row [c | r] and whose value is c, and U^V is applied to the attended latent afterwards.  So a step's cost
@@ -51,11 +53,15 @@ def heads_product(ctx, a, a_off, lda, sa, w, n, k, c, c_off, ldc, sc, heads):
 
 @MIXERS.register("latent_attention")
 class LatentAttention(Mixer):
-    """Tensor names under ``prefix``: ``q`` [H*(head_dim+rot_dim), d], ``dkv`` [R+rot_dim, d], ``dkv.norm`` [R],
-    ``uk`` [H*head_dim, R], ``uv`` [H*value_dim, R], ``o`` [d, H*value_dim]."""
+    """Tensor names under ``prefix``: ``q`` [H*(head_dim+rot_dim), d] (with ``q_rank`` Rq instead ``dq`` [Rq, d], ``dq.norm`` [Rq],
+    ``uq`` [H*(head_dim+rot_dim), Rq]), ``dkv`` [R+rot_dim, d], ``dkv.norm`` [R], ``uk`` [H*head_dim, R], ``uv`` [H*value_dim, R],
+    ``o`` [d, H*value_dim]."""
 
     def __init__(self, prefix: str, width: int, heads: int, head_dim: int, rot_dim: int, value_dim: int, kv_rank: int,
-                 eps: float, scale: Optional[float] = None, position: Optional[PartSpec] = None, rot_dims: Optional[int] = None):
+                 eps: float, scale: Optional[float] = None, position: Optional[PartSpec] = None, rot_dims: Optional[int] = None,
+                 q_rank: Optional[int] = None):
+        self.q_rank = int(q_rank) if q_rank else 0
+        self.w_uq = self.q_norm_w = None
         self.prefix, self.width = prefix, int(width)
         self.heads, self.dq, self.dr, self.dv, self.rank = int(heads), int(head_dim), int(rot_dim), int(value_dim), int(kv_rank)
         self.eps = float(eps)
@@ -68,14 +74,23 @@ class LatentAttention(Mixer):
 
     def tensor_specs(self):
         p, d, H = self.prefix, self.width, self.heads
-        return [TensorSpec(p + "q", (H * (self.dq + self.dr), d)), TensorSpec(p + "dkv", (self.rank + self.dr, d)),
+        if self.q_rank:
+            queries = [TensorSpec(p + "dq", (self.q_rank, d)), TensorSpec(p + "dq.norm", (self.q_rank,), kind="vector", init="norm"),
+                       TensorSpec(p + "uq", (H * (self.dq + self.dr), self.q_rank))]
+        else:
+            queries = [TensorSpec(p + "q", (H * (self.dq + self.dr), d))]
+        return queries + [TensorSpec(p + "dkv", (self.rank + self.dr, d)),
                 TensorSpec(p + "dkv.norm", (self.rank,), kind="vector", init="norm"),
                 TensorSpec(p + "uk", (H * self.dq, self.rank)), TensorSpec(p + "uv", (H * self.dv, self.rank)),
                 TensorSpec(p + "o", (d, H * self.dv))]
 
     def bind(self, tensors):
         p, H = self.prefix, self.heads
-        self.w_in = torch.cat([tensors[p + "q"], tensors[p + "dkv"]], dim=0).contiguous()      # one product for q and the latent
+        first = tensors[p + "dq"] if self.q_rank else tensors[p + "q"]
+        self.w_in = torch.cat([first, tensors[p + "dkv"]], dim=0).contiguous()      # one product for q (or its latent) and the latent
+        if self.q_rank:
+            self.w_uq = tensors[p + "uq"]
+            self.q_norm_w = tensors[p + "dq.norm"]
         self.norm_w = tensors[p + "dkv.norm"].float().contiguous()
         self.w_ukT = tensors[p + "uk"].view(H, self.dq, self.rank).transpose(1, 2).contiguous()  # [H, R, dq]: q^plain -> latent space
         self.w_uv = tensors[p + "uv"].view(H, self.dv, self.rank).contiguous()                   # [H, dv, R]
@@ -89,12 +104,19 @@ class LatentAttention(Mixer):
         H, dq, dr, dv, R = self.heads, self.dq, self.dr, self.dv, self.rank
         T = x.shape[0]
         width = R + dr
-        src = linear.linear(ctx, x, self.w_in)                       # [T, H*(dq+dr) + R + dr]
+        src = linear.linear(ctx, x, self.w_in)                       # [T, H*(dq+dr) + R + dr], or [T, Rq + R + dr]
+        low, low_offset = None, 0
+        if self.q_rank:
+            cq = torch.empty((T, self.q_rank), dtype=x.dtype, device=x.device)
+            ops.rms_norm_strided(src, src.shape[1], self.q_norm_w, self.eps, cq)      # the first Rq columns of every row
+            low, low_offset = src, self.q_rank
+            src = linear.linear(ctx, cq, self.w_uq)                  # [T, H*(dq+dr)]
         qabs = torch.empty((T, H, width), dtype=x.dtype, device=x.device)
         table = self.position.table(x.device) if self.position is not None else None
         ops.latent_prepare(src, ctx.tok_pos, ctx.tok_row, cache.block_table, cache.pages if cache.writes else None, qabs,
                            norm_weight=self.norm_w, eps=self.eps, H=H, dq=dq, dr=dr, R=R, ps=cache.page_size, table=table,
-                           rot_dims=self.rot_dims, interleaved=bool(getattr(self.position, "interleaved", True)), err=ctx.err)
+                           rot_dims=self.rot_dims, interleaved=bool(getattr(self.position, "interleaved", True)), low=low,
+                           low_offset=low_offset, err=ctx.err)
         # the plain query parts, carried into the latent space: qabs[t, h, :R] = q_h^plain(t) U_h^K
         heads_product(ctx, src, 0, src.shape[1], dq + dr, self.w_ukT, R, dq, qabs, 0, H * width, width, H)
         lat = torch.empty((T, H * R), dtype=x.dtype, device=x.device)

@@ -19,6 +19,11 @@ next norm adds, so the sum costs no kernel.
 feed-forward may be absent.
 
 ``residual_pre_norm`` block: x <- x + mixer(norm1(x)); x <- x + feed_forward(norm2(x)); the second sublayer may be absent.
+
+``sublayer_norm`` block: the norms sit on the sublayers' outputs and the sublayers read the stream itself,
+x <- x + norm1(mixer(x)); x <- x + norm2(feed_forward(x)) (a norm may carry a scale per column behind it, "layer scale"); the second
+sublayer may be absent.  Norm and sum are one kernel (``ops.sublayer_norm_add``), which also leaves the new stream in the compute
+type for the next sublayer.
 """
 from __future__ import annotations
 
@@ -42,6 +47,8 @@ class Pending:
     updates: tuple = ()                       # outputs of the last layer's sublayers [T, d], compute type
     extra: Optional[torch.Tensor] = None      # float32 [T, d]
     vec: Optional[torch.Tensor] = None        # float32 [d]
+    rounded: Optional[torch.Tensor] = None    # the settled stream in the compute type, when nothing above is pending and a kernel
+                                              # made it on its way (a block whose sublayers read the stream itself takes it)
 
     def empty(self) -> bool:
         return not self.updates and self.extra is None and self.vec is None
@@ -56,7 +63,8 @@ def read(ctx, x, pending: Optional[Pending], norm, rows=None, write_back=True):
         out = torch.empty((n, x.shape[1]), dtype=torch.float32, device=x.device)
         return ops.residual_norm(x, out, updates=p.updates, extra=p.extra, vec=p.vec, rows=rows, write_back=write_back)
     out = torch.empty((n, x.shape[1]), dtype=ctx.dtype, device=x.device)
-    return ops.residual_norm(x, out, updates=p.updates, extra=p.extra, vec=p.vec, weight=norm.weight32(), eps=norm.eps, kind=norm.kind,
+    bias = norm.bias32() if hasattr(norm, "bias32") else None
+    return ops.residual_norm(x, out, updates=p.updates, extra=p.extra, vec=p.vec, weight=norm.weight32(), bias=bias, eps=norm.eps, kind=norm.kind,
                              rows=rows, write_back=write_back)
 
 
@@ -178,3 +186,37 @@ class ResidualPreNormBlock(Block):
             return x, Pending((y,))
         f = read(ctx, x, Pending((y,)), self.norm2)
         return x, Pending((self.feed_forward.forward(ctx, f),))
+
+
+@BLOCKS.register("sublayer_norm")
+class SublayerNormBlock(Block):
+    """Norms on the sublayers' outputs; a scale per column behind a norm is the norm's own (``layer_norm`` with ``scale``)."""
+    roles = ("norm1", "mixer")
+    optional_roles = ("norm2", "feed_forward")
+
+    def __init__(self, parts):
+        super().__init__(parts)
+        if (self.norm2 is None) != (self.feed_forward is None):
+            raise ValueError("the second norm and the feed-forward come together or not at all")
+
+    def _settle(self, ctx, x, y, norm):
+        out = None
+        if ctx.dtype != torch.float32:
+            out = torch.empty(x.shape, dtype=ctx.dtype, device=x.device)
+        ops.sublayer_norm_add(x, y, out, weight=norm.weight32(), bias=norm.bias32() if hasattr(norm, "bias32") else None, eps=norm.eps,
+                              kind=norm.kind)
+        return x if out is None else out
+
+    def forward(self, ctx, x, pending, cache):
+        if pending is not None and pending.rounded is not None and pending.empty():
+            h = pending.rounded
+        elif ctx.dtype == torch.float32 and (pending is None or pending.empty()):
+            h = x
+        else:
+            h = torch.empty(x.shape, dtype=ctx.dtype, device=x.device)
+            p = pending or Pending()
+            ops.residual_norm(x, h, updates=p.updates, extra=p.extra, vec=p.vec)      # settles what is pending; h = x rounded once
+        h = self._settle(ctx, x, self.mixer.forward(ctx, h, cache), self.norm1)
+        if self.feed_forward is not None:
+            h = self._settle(ctx, x, self.feed_forward.forward(ctx, h), self.norm2)
+        return x, Pending(rounded=h if h is not x else None)

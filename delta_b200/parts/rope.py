@@ -12,6 +12,11 @@ reference's pairing.
 l = 2 pi / f, a frequency f is kept where l < original / high, divided by ``factor`` where l > original / low, and
 between the two blended, (1 - s) f / factor + s f with s = (original / l - low) / (high - low).
 
+``scaling`` {factor, original, fast, slow} is the other rule ("YaRN"): with pair(t) = head_dim ln(original / (2 pi t)) / (2 ln theta)
+the (fractional) pair whose wave makes t turns over the original length, lo = max(floor(pair(fast)), 0),
+hi = min(ceil(pair(slow)), head_dim - 1) and ramp_j = clamp((j - lo) / max(hi - lo, 0.001), 0, 1), pair j turns by
+f_j / factor * ramp_j + f_j (1 - ramp_j), and cos and sin are both multiplied by 0.1 ln(factor) + 1.
+
 Cos and sin are tabulated once per (head_dim, theta, scale) in 64 bit and
 rounded to 32 bit, so the kernels do no trigonometry and the angles carry no
 32-bit rounding of a large position times a small frequency.
@@ -39,8 +44,12 @@ class RotaryPositions(PositionEncoding):
         self.max_positions = int(max_positions)
         self.interleaved = bool(interleaved)
         self.scale = float(scale)
-        self.scaling = None
-        if scaling:
+        self.scaling = self.ramp = None
+        if scaling and ("fast" in scaling or "slow" in scaling):
+            self.ramp = tuple(float(scaling[k]) for k in ("factor", "original", "fast", "slow"))
+            if min(self.ramp) <= 0 or self.theta <= 1.0:
+                raise ValueError("rotary scaling: factor, original, fast and slow must be positive and the base above 1")
+        elif scaling:
             self.scaling = tuple(float(scaling[k]) for k in ("factor", "low", "high", "original"))
             if self.scaling[2] == self.scaling[1]:
                 raise ValueError("rotary scaling: 'high' and 'low' must differ")
@@ -56,16 +65,30 @@ class RotaryPositions(PositionEncoding):
             s = (original / wave - low) / (high - low)
             blend = (1.0 - s) * inv / factor + s * inv
             inv = torch.where(wave < original / high, inv, torch.where(wave > original / low, inv / factor, blend))
+        if self.ramp is not None:
+            factor, original, fast, slow = self.ramp
+
+            def pair(turns):
+                return self.head_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.theta))
+
+            lo = max(math.floor(pair(fast)), 0)
+            hi = min(math.ceil(pair(slow)), self.head_dim - 1)
+            ramp = ((j - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+            inv = inv / factor * ramp + inv * (1.0 - ramp)
         return inv
+
+    def magnitude(self) -> float:
+        """The factor on cos and sin (1 unless the scaling rule has one)."""
+        return 0.1 * math.log(self.ramp[0]) + 1.0 if self.ramp is not None else 1.0
 
     def table_cpu(self) -> torch.Tensor:
         """[max_positions, head_dim/2, 2] float32: cos and sin of every angle."""
         inv = self.frequencies()
         ang = torch.arange(self.max_positions, dtype=torch.float64)[:, None] * inv[None, :]
-        return torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).to(torch.float32).contiguous()
+        return (torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1) * self.magnitude()).to(torch.float32).contiguous()
 
     def table(self, device) -> torch.Tensor:
-        key = (self.head_dim, self.theta, self.scale, self.scaling, self.max_positions, str(device))
+        key = (self.head_dim, self.theta, self.scale, self.scaling, self.ramp, self.max_positions, str(device))
         if key not in _TABLES:
             _TABLES[key] = self.table_cpu().to(device)
         return _TABLES[key]
