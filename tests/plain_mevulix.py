@@ -144,10 +144,12 @@ def attention(h, W, p, m, eps, kv):
     cap = m.get("softcap")
     if cap:
         s = float(cap) * torch.tanh(s / float(cap))
-    rel = W[p + "rel"].to(F)
-    rows = rel.shape[0]
-    bucket = torch.tensor([[distance_bucket(i - j, rows, float(m["bias_max"])) if j <= i else 0 for j in range(T)] for i in range(T)])
-    s = s + rel[bucket].permute(2, 0, 1)
+    if m.get("bias_max") is not None:
+        rel = W[p + "rel"].to(F)
+        rows = rel.shape[0]
+        by_distance = [distance_bucket(n, rows, float(m["bias_max"])) for n in range(T)]
+        bucket = torch.tensor([[by_distance[i - j] if j <= i else 0 for j in range(T)] for i in range(T)])
+        s = s + rel[bucket].permute(2, 0, 1)
     visible = (pos[None, :] <= pos[:, None])[None]
     w = softmax_with_sink(s, visible, W[p + "sink"])
     y = rnd(torch.einsum("hij,jhd->ihd", w, v)).reshape(T, H * dv)
@@ -185,11 +187,19 @@ def gated(h, W, p, act):
     return lin(rnd(act(lin(h, W[p + "gate"])) * lin(h, W[p + "up"])), W[p + "down"])
 
 
+MARGINS = None      # a list: every call of ``experts`` appends its tokens' margins [T] here and their choices [T, top] to CHOICES
+CHOICES = []
+
+
 def experts(h, W, p, mlp):
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
     z = h @ W[p + "router"].to(F).T
     score = torch.sigmoid(z)
-    chosen = torch.topk(z, top, dim=-1).indices          # the order of z is the order of sigmoid(z)
+    ranked = torch.sort(z, dim=-1, descending=True, stable=True)      # the order of z is the order of sigmoid(z)
+    chosen = ranked.indices[:, :top]
+    if MARGINS is not None:      # how far the last chosen expert is ahead of the first one left out, and the choice as a set
+        MARGINS.append(ranked.values[:, top - 1] - ranked.values[:, top] if top < E else torch.full_like(z[:, 0], 9.0))
+        CHOICES.append(torch.sort(chosen, dim=-1).values)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e in chosen[t].tolist():
@@ -232,5 +242,5 @@ def forward(cfg: dict, W: dict, tokens):
             x = x + layer_norm(f, W[p + "norm2"], W[p + "norm2.b"], eps) * W[p + "ls2"].to(F)
         after.append(x.clone())
     h = rnd(layer_norm(x, W["final.norm"], W["final.norm.b"], eps))
-    logits = (h @ W["head"].to(F).T) * float(cfg["logit_scale"])
+    logits = (h @ W["head"].to(F).T) * float(cfg.get("logit_scale", 1.0))
     return logits, torch.stack(after)
