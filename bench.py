@@ -56,6 +56,10 @@ Other workloads (``--workload``), each printing one JSON line of the same shape:
                linear attention with a decay per head, mixtures of experts; random weights at widths ``--width``)
                beside the Yi architecture, measured as the roletar workload is
 
+  mevulix      the Mevulix design (norms on the sublayers' outputs, latent attention with a query latent, attention with
+               capped scores and biases by distance, gelu-gated feed-forwards, experts whose weights multiply their input)
+               beside Yi, Pibalorn and Roletar, measured as the roletar workload is
+
 ``--impl reference`` runs the unmodified hoenza/DELTA engine (baseline/reference_arm.py) on the
 default workload and prints its line.
 """
@@ -436,13 +440,32 @@ def mufalix_config(d: int) -> dict:
                 layers=[dict(mem, mlp=experts), dict(pair, mlp=experts), dict(mem, mlp=experts), dict(pair, mlp=experts)])
 
 
+def mevulix_config(d: int) -> dict:
+    """A Mevulix model with layers of the sizes of a real model of width d: latent attention (d/128 heads of 128 plain and 64 rotated
+    entries, latents of 256 for keys and values and 3d/8 for queries, ramp-scaled rotary positions) and grouped-query attention
+    (d/128 heads on d/512 key-value heads, capped scores, a bias table of 32 rows up to distance 1,024, a query temperature), one
+    of the attention layers reading another's keys and values; dense gated feed-forwards and mixtures of 16 experts (4 chosen, d/2
+    wide each, and a shared expert) take turns."""
+    H = d // 128
+    lat = dict(type="latent_attention", mixer=dict(heads=H, dim=128, rot_dim=64, vdim=128, kv_rank=256, q_rank=3 * d // 8, scale=0.07,
+                                                   rot=dict(base=500000.0, dims=64, scaling=dict(factor=8.0, original=4096, fast=32.0, slow=1.0))))
+    att = dict(heads=H, kv_heads=max(1, H // 4), dim=128, vdim=128, scale=0.09, softcap=50.0, q_temp=dict(coef=0.1, every=512),
+               bias_max=1024, bias_rows=32)
+    experts = dict(kind="moe", router=dict(experts=16, top=4), expert=dict(ff=d // 2), shared=dict(ff=d // 2))
+    dense = dict(kind="dense", ff=(8 * d // 3 + 255) // 256 * 256)
+    return dict(architecture="Mevulix", vocab=32000, width=d, norm=dict(eps=1e-5), logit_scale=0.5,
+                layers=[dict(lat, mlp=experts), dict(type="attention", mixer=att, mlp=dense), dict(lat, mlp=experts),
+                        dict(type="attention", mixer=dict(att, kv_from=1), mlp=experts), dict(lat, mlp=dense),
+                        dict(type="attention", mixer=att, mlp=experts)])
+
+
 def roletar_workload(args) -> int:
     return design_workload(args, "roletar")
 
 
 def design_workload(args, design: str) -> int:
-    """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 at context 2,048) of a design (Roletar, Pibalorn, Mufalix) beside the
-    Yi architecture at equal width and layer count (Mufalix also beside Pibalorn, the closest design), through ``ModelRunner.step``, timed with CUDA events after warm-up with
+    """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 at context 2,048) of a design (Roletar, Pibalorn, Mufalix, Mevulix) beside the
+    Yi architecture at equal width and layer count (Mufalix also beside Pibalorn, the closest design; Mevulix beside Pibalorn and Roletar), through ``ModelRunner.step``, timed with CUDA events after warm-up with
     the L2 flushed before every timed step; then every launcher's share of one such step, with the fraction of the measured
     peaks that the design's own kernels and their Yi counterparts reach."""
     import torch
@@ -523,13 +546,16 @@ def design_workload(args, design: str) -> int:
 
     launches = 0
     for d in args.width:
-        rc = {"roletar": roletar_config, "pibalorn": pibalorn_config, "mufalix": mufalix_config}[design](d)
+        rc = {"roletar": roletar_config, "pibalorn": pibalorn_config, "mufalix": mufalix_config, "mevulix": mevulix_config}[design](d)
         runs = 6
         yc = yi_like_config(d, runs)
         a, b = measure(rc, rc["vocab"]), measure(yc, yc["vocab_size"])
-        if design == "mufalix":     # the closest design of the engine (32-bit stream, a recurrent state, experts, a repeated span) as well
+        if design in ("mufalix", "mevulix"):     # the closest design of the engine (32-bit stream, layer norms, experts beside a shared one) as well
             pc = pibalorn_config(d)
             c = measure(pc, pc["vocab"])
+        if design == "mevulix":     # and the one whose mixers are the closest (latent attention, attention with a sink over a cache of rows)
+            oc = roletar_config(d)
+            c2 = measure(oc, oc["vocab"])
         launches += a["launches_per_decode_step"]
         H = d // 128
         # what the kernels of one step have to move or compute, per launcher (prefill of T tokens unless said otherwise)
@@ -578,6 +604,33 @@ def design_workload(args, design: str) -> int:
                 "experts_gemm_tc": (0, 2 * T * top * 2 * d * F * n_moe),
                 "attention_rows_mma": (0, 4 * 128 * H * seen * n_pair),
             }
+        if design == "mevulix":
+            G, top, F, Fd, Rq = max(1, H // 4), 4, d // 2, (8 * d // 3 + 255) // 256 * 256, 3 * d // 8
+            n_lat, n_att, n_own, n_moe, n_dense = 3, 3, 2, 4, 2      # latent layers, attention layers, of which with keys of their own, mixtures, dense
+            pairs = T * (T + 1) // 2
+            work = {
+                "sublayer_norm_add": ((2 * d * 4 + 2 * d * 2) * T * (2 * runs), 0),
+                "residual_norm": ((d * 4 + d * 2) * T, 0),
+                "rms_norm_strided": (2 * Rq * 2 * T * n_lat, 0),
+                "latent_prepare": ((2 * H * 64 + 2 * 320) * 2 * T * n_lat, 0),
+                "rows_append_unit": (((2 * H + 4 * G) * n_own + 2 * H * (n_att - n_own)) * 128 * 2 * T, 0),
+                "glu_clamped": (3 * (Fd * n_dense + F * n_moe) * 2 * T, 0),
+                "experts_scale_rows": ((1 + top) * d * 2 * T * n_moe, 0),
+                "experts_gather": (2 * top * d * 2 * T * n_moe, 0),
+                "experts_combine": ((top * d * 4 + 2 * d * 2) * T * n_moe, 0),
+                "experts_gemm_tc": (0, 2 * T * top * 3 * d * F * n_moe),
+                "library batched product": (0, 2 * T * H * (128 * 256 + 256 * 128) * n_lat),
+                "gemm_nt_plain_batched": (0, 2 * T * H * (128 * 256 + 256 * 128) * n_lat),
+                "attention_rows_mma": (0, 2 * H * (320 + 256) * pairs * n_lat + 4 * 128 * H * pairs * n_att),
+            }
+        roletar_work = {
+            "stream_norm": ((2 * S * d * 4 + 2 * d * 2) * T * (2 * runs), 0),
+            "latent_prepare": ((H * 192 + 320 + 320 + H * 64) * 2 * T * 4, 0),
+            "rows_append": ((H + 2 * max(1, H // 4)) * 128 * 2 * T, 0),
+            "gemm_nt_plain_batched": (0, 2 * T * H * (128 * 256 + 256 * 128) * 4),
+            "library batched product": (0, 2 * T * H * (128 * 256 + 256 * 128) * 4),
+            "attention_rows_mma": (0, 4 * (2 * H * (320 + 256) * T * (T + 1) // 2) + 2 * H * 256 * (1024 * T - 1024 * 1023 // 2)),
+        }
         yi_work = {
             "rms_norm": (4 * d * 2 * T * (2 * runs) , 0),
             "silu_mul": (3 * yc["intermediate_size"] * 2 * T * runs, 0),
@@ -612,7 +665,12 @@ def design_workload(args, design: str) -> int:
                              "decode_ms": c["decode_ms"], "decode_graph_ms": c["decode_graph_ms"],
                              "launches_per_decode_step": c["launches_per_decode_step"],
                              "prefill_launchers": fractions(c["prefill_launchers"], pibalorn_work()),
-                             "decode_launchers": fractions(c["decode_launchers"], {})}} if design == "mufalix" else {}),
+                             "decode_launchers": fractions(c["decode_launchers"], {})}} if design in ("mufalix", "mevulix") else {}),
+            **({"roletar": {"prefill_tok_s": T / c2["prefill_ms"] * 1e3, "prefill_ms": c2["prefill_ms"], "decode_tok_s": B / c2["decode_ms"] * 1e3,
+                            "decode_ms": c2["decode_ms"], "decode_graph_ms": c2["decode_graph_ms"],
+                            "launches_per_decode_step": c2["launches_per_decode_step"],
+                            "prefill_launchers": fractions(c2["prefill_launchers"], roletar_work),
+                            "decode_launchers": fractions(c2["decode_launchers"], {})}} if design == "mevulix" else {}),
             "config": {"width": d, "layer_runs": runs, "prefill_tokens": T, "decode_batch": B, "decode_context": CTX,
                        "l2": "flushed before every timed step"}}
     first = out["sizes"][str(args.width[0])]
@@ -638,8 +696,9 @@ def main() -> int:
     ap.add_argument("--enable_selective_cache", action="store_true", help="DELTA on (not the default run)")
     ap.add_argument("--full_cache_layers", nargs="+", type=int, default=[0, 1, 2, 14, 22])
     ap.add_argument("--subset_cache_size", type=int, default=64)
-    ap.add_argument("--workload", choices=["decode", "baseline", "yi9b-long", "yi34b-mixed", "grown", "long-prompt", "roletar", "pibalorn", "mufalix"], default="decode")
-    ap.add_argument("--width", type=int, nargs="+", default=[2048, 4096], help="--workload roletar / pibalorn / mufalix: the model widths that are measured")
+    ap.add_argument("--workload", choices=["decode", "baseline", "yi9b-long", "yi34b-mixed", "grown", "long-prompt", "roletar", "pibalorn", "mufalix", "mevulix"],
+                    default="decode")
+    ap.add_argument("--width", type=int, nargs="+", default=[2048, 4096], help="--workload roletar / pibalorn / mufalix / mevulix: the model widths that are measured")
     ap.add_argument("--generate", type=int, default=None, help="tokens generated per request in the other workloads (default: what the workload names)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -649,7 +708,7 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
-    if args.workload in ("roletar", "pibalorn", "mufalix"):
+    if args.workload in ("roletar", "pibalorn", "mufalix", "mevulix"):
         return design_workload(args, args.workload)
     if args.workload != "decode":
         return other_workload(args)

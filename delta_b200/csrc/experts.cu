@@ -10,7 +10,8 @@
 //                   nothing about the routing is read on the host;
 //   experts_gemm    for every tile the product of its rows with its expert's matrix.  First product: rows are gathered
 //                   from the tokens, the matrix is [gate (F) | up (F)] x d, and the gated activation is applied before
-//                   the result is stored at the row's place in the sorted order.  Second product: rows are read in the
+//                   the result is stored at the row's place in the sorted order (row_scale: the product of a slot is multiplied by
+//                   the slot's weight first, which is what an expert that reads weight * x gets).  Second product: rows are read in the
 //                   sorted order and the result goes to the slot's own place, in 32 bit;
 //   experts_combine out[t] = sum_j weight[t][j] * z[t*top + j]  (+ sigmoid(gate logit of t) * shared[t]), summed in 32 bit in
 //                   the order of the choices, so the result does not depend on what else is in the batch.
@@ -269,7 +270,8 @@ __device__ __forceinline__ float relu_squared(float x) { return x > 0.f ? x * x 
 template <typename T, int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS)
 experts_gemm_kernel(const T* __restrict__ A, const T* __restrict__ W, void* __restrict__ out, const int* __restrict__ sorted,
-                    const int* __restrict__ tile_expert, int top, int N, int K, float limit, float alpha, float shift) {
+                    const int* __restrict__ tile_expert, int top, int N, int K, float limit, float alpha, float shift,
+                    const float* __restrict__ row_scale) {
   constexpr bool ACT = MODE == 1, FIRST = MODE != 0;
   const int tile = blockIdx.y;
   const int e = tile_expert[tile];
@@ -330,16 +332,17 @@ experts_gemm_kernel(const T* __restrict__ A, const T* __restrict__ W, void* __re
     const int lr = 4 * ty + r;
     const int s = sorted[p0 + lr];
     if (s < 0) continue;
+    const float rs = (FIRST && row_scale != nullptr) ? row_scale[s] : 1.f;      // (w x) W^T = w (x W^T)
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       const int n = n0 + tx + 16 * c;
       if (n >= N) continue;
       if (ACT) {
         // the two products are rounded to the element type before the activation, as separate products would be
-        const float g = to_f32<T>(from_f32<T>(acc[0][r][c])), u = to_f32<T>(from_f32<T>(acc[ACT ? 1 : 0][r][c]));
+        const float g = to_f32<T>(from_f32<T>(acc[0][r][c] * rs)), u = to_f32<T>(from_f32<T>(acc[ACT ? 1 : 0][r][c] * rs));
         ((T*)out)[(size_t)(p0 + lr) * N + n] = from_f32<T>(glu_value(g, u, limit, alpha, shift));
       } else if (FIRST) {
-        ((T*)out)[(size_t)(p0 + lr) * N + n] = from_f32<T>(relu_squared(to_f32<T>(from_f32<T>(acc[0][r][c]))));
+        ((T*)out)[(size_t)(p0 + lr) * N + n] = from_f32<T>(relu_squared(to_f32<T>(from_f32<T>(acc[0][r][c] * rs))));
       } else {
         ((float*)out)[(size_t)s * N + n] = acc[0][r][c];
       }
@@ -361,7 +364,7 @@ template <int MODE>
 __global__ void __launch_bounds__(256)
 experts_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W, void* __restrict__ out,
                         const int* __restrict__ sorted, const int* __restrict__ tile_expert, int top, int N, int K, float limit,
-                        float alpha, float shift) {
+                        float alpha, float shift, const float* __restrict__ row_scale) {
   constexpr bool ACT = MODE == 1, FIRST = MODE != 0;
   const int tile = blockIdx.y;
   const int e = tile_expert[tile];
@@ -456,6 +459,7 @@ experts_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16
       const int lr = wm * 32 + i * 16 + g + half * 8;
       const int s = sorted[p0 + lr];
       if (s < 0) continue;
+      const float rs = (FIRST && row_scale != nullptr) ? row_scale[s] : 1.f;      // (w x) W^T = w (x W^T)
       if (ACT) {
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
@@ -463,8 +467,8 @@ experts_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16
 #pragma unroll
           for (int q = 0; q < 2; ++q) {
             if (n + q >= N) continue;
-            const float gv = __bfloat162float(__float2bfloat16_rn(acc[i][j][half * 2 + q]));
-            const float uv = __bfloat162float(__float2bfloat16_rn(acc[i][j + 2][half * 2 + q]));
+            const float gv = __bfloat162float(__float2bfloat16_rn(acc[i][j][half * 2 + q] * rs));
+            const float uv = __bfloat162float(__float2bfloat16_rn(acc[i][j + 2][half * 2 + q] * rs));
             ((__nv_bfloat16*)out)[(size_t)(p0 + lr) * N + n + q] = __float2bfloat16_rn(glu_value(gv, uv, limit, alpha, shift));
           }
         }
@@ -477,7 +481,7 @@ experts_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16
             if (n + q >= N) continue;
             if (FIRST)      // the product rounded to bfloat16 first, as a separate product would be
               ((__nv_bfloat16*)out)[(size_t)(p0 + lr) * N + n + q] =
-                  __float2bfloat16_rn(relu_squared(__bfloat162float(__float2bfloat16_rn(acc[i][j][half * 2 + q]))));
+                  __float2bfloat16_rn(relu_squared(__bfloat162float(__float2bfloat16_rn(acc[i][j][half * 2 + q] * rs))));
             else
               ((float*)out)[(size_t)s * N + n + q] = acc[i][j][half * 2 + q];
           }
@@ -488,24 +492,26 @@ experts_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16
 
 // rows[p] = x[sorted[p] / top] (zeros where sorted[p] < 0): the tokens in the sorted order, for products that want their rows
 // side by side (csrc/gemm_tc.cu).  K is a multiple of 8.
+// row_scale (or null): rows[p] = row_scale[sorted[p]] * x[sorted[p] / top], rounded once: a choice's weight multiplies what its
+// expert reads.
 __global__ void experts_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ sorted, int top,
-                                      __nv_bfloat16* __restrict__ rows, int K) {
+                                      __nv_bfloat16* __restrict__ rows, int K, const float* __restrict__ row_scale) {
   const int p = blockIdx.x;
   const int s = sorted[p];
   const uint4* src = s < 0 ? nullptr : reinterpret_cast<const uint4*>(x + (size_t)(s / top) * K);
   uint4* dst = reinterpret_cast<uint4*>(rows + (size_t)p * K);
-  for (int c = threadIdx.x; c < K / 8; c += blockDim.x) dst[c] = src ? src[c] : make_uint4(0u, 0u, 0u, 0u);
-}
-
-// xs[t * top + j] = weight[t][j] * x[t], rounded once: the experts' inputs when a choice's weight multiplies what the expert
-// reads (not what it gives).
-template <typename T>
-__global__ void experts_scale_rows_kernel(const T* __restrict__ x, const float* __restrict__ weight, T* __restrict__ xs, int d) {
-  const size_t slot = (size_t)blockIdx.x * gridDim.y + blockIdx.y;      // grid (T, top)
-  const T* src = x + (size_t)blockIdx.x * d;
-  T* dst = xs + slot * d;
-  const float wt = weight[slot];
-  for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = from_f32<T>(wt * to_f32<T>(src[i]));
+  if (src == nullptr || row_scale == nullptr) {
+    for (int c = threadIdx.x; c < K / 8; c += blockDim.x) dst[c] = src ? src[c] : make_uint4(0u, 0u, 0u, 0u);
+    return;
+  }
+  const float w = row_scale[s];
+  for (int c = threadIdx.x; c < K / 8; c += blockDim.x) {
+    float v[8];
+    load8<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(src + c), v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] *= w;
+    store8<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(dst + c), v);
+  }
 }
 
 template <typename T>
@@ -594,8 +600,11 @@ extern "C" int dk_experts_align(const int* choice, int n_slots, int E, int* sort
   return dk_check_launch("experts_align");
 }
 
+// row_scale (float [slots] or null): in a first product (act != 0) the row of slot s is multiplied by row_scale[s] before the
+// activation, as if the expert had read row_scale[s] * x.
 extern "C" int dk_experts_gemm(const void* A, const void* W, void* out, const int* sorted, const int* tile_expert, int max_tiles, int top,
-                               int N, int K, int act, float limit, float alpha, float shift, int dtype, cudaStream_t stream) {
+                               int N, int K, int act, float limit, float alpha, float shift, const float* row_scale, int dtype,
+                               cudaStream_t stream) {
   if (max_tiles == 0) return 0;
   DK_REQUIRE(max_tiles > 0 && N > 0 && K > 0 && top > 0, "experts_gemm: bad sizes tiles=%d N=%d K=%d top=%d", max_tiles, N, K, top);
   DK_REQUIRE(act >= 0 && act <= 2, "experts_gemm: activation %d is not known (0 none, 1 gated, 2 relu squared)", act);
@@ -616,7 +625,7 @@ extern "C" int dk_experts_gemm(const void* A, const void* W, void* out, const in
     }
 #define MMA_LAUNCH(MODE)                                                                                                          \
   experts_gemm_mma_kernel<MODE><<<mgrid, 256, MMA_SMEM, stream>>>((const __nv_bfloat16*)A, (const __nv_bfloat16*)W, out, sorted, tile_expert, \
-                                                                  top, N, K, limit, alpha, shift)
+                                                                  top, N, K, limit, alpha, shift, row_scale)
     if (act == 1) MMA_LAUNCH(1);
     else if (act == 2) MMA_LAUNCH(2);
     else MMA_LAUNCH(0);
@@ -626,9 +635,9 @@ extern "C" int dk_experts_gemm(const void* A, const void* W, void* out, const in
   const dim3 grid((N + TILE_N - 1) / TILE_N, max_tiles);
 #define LAUNCH(T)                                                                                                                  \
   do {                                                                                                                             \
-    if (act == 1) experts_gemm_kernel<T, 1><<<grid, GEMM_THREADS, 0, stream>>>((const T*)A, (const T*)W, out, sorted, tile_expert, top, N, K, limit, alpha, shift); \
-    else if (act == 2) experts_gemm_kernel<T, 2><<<grid, GEMM_THREADS, 0, stream>>>((const T*)A, (const T*)W, out, sorted, tile_expert, top, N, K, limit, alpha, shift); \
-    else experts_gemm_kernel<T, 0><<<grid, GEMM_THREADS, 0, stream>>>((const T*)A, (const T*)W, out, sorted, tile_expert, top, N, K, limit, alpha, shift);    \
+    if (act == 1) experts_gemm_kernel<T, 1><<<grid, GEMM_THREADS, 0, stream>>>((const T*)A, (const T*)W, out, sorted, tile_expert, top, N, K, limit, alpha, shift, row_scale); \
+    else if (act == 2) experts_gemm_kernel<T, 2><<<grid, GEMM_THREADS, 0, stream>>>((const T*)A, (const T*)W, out, sorted, tile_expert, top, N, K, limit, alpha, shift, row_scale); \
+    else experts_gemm_kernel<T, 0><<<grid, GEMM_THREADS, 0, stream>>>((const T*)A, (const T*)W, out, sorted, tile_expert, top, N, K, limit, alpha, shift, row_scale);    \
   } while (0)
   if (dtype == DK_F32) LAUNCH(float);
   else if (dtype == DK_BF16) LAUNCH(__nv_bfloat16);
@@ -637,11 +646,12 @@ extern "C" int dk_experts_gemm(const void* A, const void* W, void* out, const in
   return dk_check_launch("experts_gemm");
 }
 
-extern "C" int dk_experts_gather(const void* x, const int* sorted, int top, void* rows, int capacity, int K, cudaStream_t stream) {
+extern "C" int dk_experts_gather(const void* x, const int* sorted, int top, void* rows, int capacity, int K, const float* row_scale,
+                                 cudaStream_t stream) {
   if (capacity == 0) return 0;
   DK_REQUIRE(capacity > 0 && K > 0 && K % 8 == 0 && top > 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)rows % 16) == 0,
              "experts_gather: bad arguments capacity=%d K=%d top=%d", capacity, K, top);
-  experts_gather_kernel<<<capacity, K >= 2048 ? 256 : 128, 0, stream>>>((const __nv_bfloat16*)x, sorted, top, (__nv_bfloat16*)rows, K);
+  experts_gather_kernel<<<capacity, K >= 2048 ? 256 : 128, 0, stream>>>((const __nv_bfloat16*)x, sorted, top, (__nv_bfloat16*)rows, K, row_scale);
   return dk_check_launch("experts_gather");
 }
 
@@ -657,16 +667,4 @@ extern "C" int dk_experts_combine(const float* z, const float* weight, int top, 
                                                                       (__nv_bfloat16*)out, d);
   else DK_REQUIRE(false, "experts_combine: unknown dtype %d", dtype);
   return dk_check_launch("experts_combine");
-}
-
-extern "C" int dk_experts_scale_rows(const void* x, const float* weight, void* xs, int T_, int top, int d, int dtype, cudaStream_t stream) {
-  if (T_ == 0) return 0;
-  DK_REQUIRE(T_ > 0 && top > 0 && top <= MAX_TOP && d > 0, "experts_scale_rows: bad sizes T=%d top=%d d=%d", T_, top, d);
-  const dim3 grid(T_, top);
-  const int threads = d >= 1024 ? 256 : 128;
-  if (dtype == DK_F32) experts_scale_rows_kernel<float><<<grid, threads, 0, stream>>>((const float*)x, weight, (float*)xs, d);
-  else if (dtype == DK_BF16)
-    experts_scale_rows_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((const __nv_bfloat16*)x, weight, (__nv_bfloat16*)xs, d);
-  else DK_REQUIRE(false, "experts_scale_rows: unknown dtype %d", dtype);
-  return dk_check_launch("experts_scale_rows");
 }

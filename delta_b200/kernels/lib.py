@@ -117,13 +117,12 @@ _SIGNATURES = {
     "dk_router_topk": [P, I, P, P, I, I, I, P],
     "dk_router": [P, P, P, P, P, I, I, I, I, I, P, F, I, I, P],
     "dk_experts_align": [P, I, I, P, I, P, I, I, P],
-    "dk_experts_gather": [P, P, I, P, I, I, P],
+    "dk_experts_gather": [P, P, I, P, I, I, P, P],
     "dk_experts_gemm_tc_supported": [I, I, I],
     "dk_experts_gemm_tc": [P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, F, P, P],
-    "dk_experts_gemm": [P, P, P, P, P, I, I, I, I, I, F, F, F, I, P],
+    "dk_experts_gemm": [P, P, P, P, P, I, I, I, I, I, F, F, F, P, I, P],
     "dk_experts_combine": [P, P, I, P, P, I, P, I, I, I, P],
     "dk_experts_tile_rows": [],
-    "dk_experts_scale_rows": [P, P, P, I, I, I, I, P],
 }
 
 

@@ -988,10 +988,12 @@ def experts_align(choice, experts, sorted_slots, tile_expert, tile_rows=None):
              "experts_align")
 
 
-def experts_gather(x, sorted_slots, top, rows):
-    """rows[p] = x[sorted_slots[p] // top] (zeros where the slot is -1); bfloat16, the width a multiple of 8."""
+def experts_gather(x, sorted_slots, top, rows, row_scale=None):
+    """rows[p] = x[sorted_slots[p] // top] (zeros where the slot is -1); bfloat16, the width a multiple of 8.  ``row_scale`` (float32,
+    one entry a slot): rows[p] = row_scale[slot] * x[slot // top], rounded once."""
     _l.check(_l.load().dk_experts_gather(_ptr(x, "x", torch.bfloat16), _ptr(sorted_slots, "sorted_slots", torch.int32), int(top),
-                                         _ptr(rows, "rows", torch.bfloat16), rows.shape[0], x.shape[1], _stream()), "experts_gather")
+                                         _ptr(rows, "rows", torch.bfloat16), rows.shape[0], x.shape[1],
+                                         _ptr(row_scale, "row_scale", torch.float32), _stream()), "experts_gather")
     return rows
 
 
@@ -1013,27 +1015,21 @@ def experts_gemm_tc(rows, w, out, tile_expert, tile_rows, *, n, row_map=None, gl
     return out
 
 
-def experts_gemm(a, w, out, sorted_slots, tile_expert, *, top, n, k, act=False, limit=-1.0, alpha=1.702, shift=1.0):
+def experts_gemm(a, w, out, sorted_slots, tile_expert, *, top, n, k, act=False, limit=-1.0, alpha=1.702, shift=1.0, row_scale=None):
     """For every tile of rows its expert's product (see ``csrc/experts.cu``).  ``act`` False: ``a`` holds the rows in sorted order, the
     result goes to the slots in 32 bit.  ``act`` True / "gated": rows gathered from the tokens, ``w`` [E, 2n, k] (gate rows, then up rows),
-    the gated activation.  ``act`` "relu_squared": rows gathered, ``w`` [E, n, k], relu(product)^2."""
+    the gated activation.  ``act`` "relu_squared": rows gathered, ``w`` [E, n, k], relu(product)^2.  ``row_scale`` (float32, one entry a
+    slot; with an activation only): the product of slot s is multiplied by row_scale[s] before the activation, which is what an expert
+    that read row_scale[s] * x would have got."""
+    if row_scale is not None and not act:
+        raise KernelError("experts_gemm: a scale per row belongs to the first product")
     code = {False: 0, True: 1, "gated": 1, "relu_squared": 2}.get(act)
     if code is None:
         raise KernelError(f"experts_gemm: unknown activation '{act}'")
     _l.check(_l.load().dk_experts_gemm(_ptr(a, "a"), _ptr(w, "w", a.dtype), _ptr(out, "out"), _ptr(sorted_slots, "sorted_slots", torch.int32),
                                        _ptr(tile_expert, "tile_expert", torch.int32), tile_expert.numel(), int(top), int(n), int(k),
-                                       code, float(limit), float(alpha), float(shift), dtype_code(a.dtype), _stream()), "experts_gemm")
-
-
-def experts_scale_rows(x, weight, out):
-    """out[t * top + j] = weight[t, j] * x[t], rounded once to the type of x."""
-    T, d = x.shape
-    top = weight.shape[1]
-    if tuple(out.shape) != (T * top, d) or weight.shape[0] != T:
-        raise KernelError(f"experts_scale_rows: {T} tokens with {top} weights each do not give rows of shape {tuple(out.shape)}")
-    _l.check(_l.load().dk_experts_scale_rows(_ptr(x, "x"), _ptr(weight, "weight", torch.float32), _ptr(out, "out", x.dtype), T, top, d,
-                                             dtype_code(x.dtype), _stream()), "experts_scale_rows")
-    return out
+                                       code, float(limit), float(alpha), float(shift), _ptr(row_scale, "row_scale", torch.float32),
+                                       dtype_code(a.dtype), _stream()), "experts_gemm")
 
 
 def experts_combine(z, weight, out, shared=None, gate_logit=None, gate_stride=0, top=None):

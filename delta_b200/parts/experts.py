@@ -14,8 +14,8 @@ the shared expert's gate row are one matrix, so one product gives both.
 Options: ``scoring`` "sigmoid": scores s = sigmoid(z); the ``top`` largest of s + correction (a tensor ``correction`` [E] when
 ``correction`` is set) are chosen, and the weights are the chosen s (without the correction) divided by their sum (+ 1e-20), times
 ``route_scale``; ``normalize`` False: the chosen s themselves, times ``route_scale``.  ``weight_input``: a choice's weight multiplies
-what its expert reads, out = sum expert(weight * h), not what it gives (the rows weight * h are made first, rounded once to the
-compute type).  ``shared`` {intermediate, limit, alpha, shift, gate}: ``gate`` False leaves the shared expert's sigmoid gate (and the
+what its expert reads, out = sum expert(weight * h), not what it gives: since (w h) W^T = w (h W^T), the first product's result is
+multiplied by the weight before the activation (the tcgen05 path multiplies the rows as it gathers them).  ``shared`` {intermediate, limit, alpha, shift, gate}: ``gate`` False leaves the shared expert's sigmoid gate (and the
 tensor ``shared.sg``) out, so it is added as it is.  ``activation`` "relu_squared": an expert is  W_down relu(W_up h)^2  with no gate branch.  ``wide_output``: the
 weighted sum is handed on in 32 bit (for a 32-bit residual stream), not rounded to the compute type.
 """
@@ -107,10 +107,8 @@ class Experts(FeedForward):
                    normalize=self.normalize)
         act = "gated" if self.gated else "relu_squared"
         slots = T * top
-        tokens = x
-        if self.weight_input:      # every slot reads a row of its own, weight * h; from here on a "token" is a slot
-            x = ops.experts_scale_rows(x, weight, torch.empty((slots, d), dtype=x.dtype, device=dev))
-            weight, top = None, 1
+        # weight_input: a slot's weight goes into the first product (or into the gathered rows), and the sum at the end has none
+        row_scale = weight.view(-1) if self.weight_input else None
         # many rows an expert (prompt portions): tiles of 128 rows through the tcgen05 product; else tiles of 64 through warp-level MMA
         many = (x.dtype == torch.bfloat16 and "products" not in ctx.plain_kernels and slots >= TC_ROWS_PER_EXPERT * E and
                 ops.experts_gemm_tc_supported(F, d, self.gated) and ops.experts_gemm_tc_supported(d, F, False))
@@ -122,18 +120,19 @@ class Experts(FeedForward):
         y = torch.empty((capacity, F), dtype=x.dtype, device=dev)
         out_slots = torch.empty((slots, d), dtype=f32, device=dev)
         if many:
-            rows = ops.experts_gather(x, sorted_slots, top, torch.empty((capacity, d), dtype=x.dtype, device=dev))
+            rows = ops.experts_gather(x, sorted_slots, top, torch.empty((capacity, d), dtype=x.dtype, device=dev), row_scale=row_scale)
             ops.experts_gemm_tc(rows, self.w1, y, tile_expert, tile, n=F, glu=True if self.gated else act, limit=self.limit, alpha=self.alpha, shift=self.shift,
                                 err=ctx.err)
             ops.experts_gemm_tc(y, self.w2, out_slots, tile_expert, tile, n=d, row_map=sorted_slots, err=ctx.err)
         else:
             ops.experts_gemm(x, self.w1, y, sorted_slots, tile_expert, top=top, n=F, k=d, act=act, limit=self.limit, alpha=self.alpha,
-                             shift=self.shift)
+                             shift=self.shift, row_scale=row_scale)
             ops.experts_gemm(y, self.w2, out_slots, sorted_slots, tile_expert, top=top, n=d, k=F)
         out = torch.empty((T, d), dtype=f32 if self.wide_output else x.dtype, device=dev)     # wide: the weighted sum unrounded
-        top = self.top
+        if self.weight_input:
+            weight = None
         if self.shared is not None:
-            s = self.shared.forward(ctx, tokens)
+            s = self.shared.forward(ctx, x)
             ops.experts_combine(out_slots, weight, out, shared=s, gate_logit=(z.data_ptr() + E * 4) if self.shared_gate else None,
                                 gate_stride=z.shape[1], top=top)
         else:

@@ -392,12 +392,12 @@ def test_attention_kernels_with_a_cap_and_biases_by_distance(case):
     tok_pos = torch.tensor([starts[r] + j for r, n in enumerate(lens) for j in range(n)], dtype=torch.int32)
     q_start = torch.tensor([sum(lens[:r]) for r in range(rows)], dtype=torch.int32)
     out = torch.full((T, H * dv), float("nan"), dtype=dtype, device=DEV)
-    to = lambda t: t.to(DEV)      # noqa: E731
-    params = ops.row_attn_params(q=to(q), q_stride=H * dk, q_head_stride=dk, out=out, cache=to(cache), block_table=to(perm), tok_row=to(tok_row),
-                                 tok_pos=to(tok_pos), row_q_start=to(q_start), row_q_len=to(torch.tensor(lens, dtype=torch.int32)),
-                                 row_pos_start=to(torch.tensor(starts, dtype=torch.int32)), H=H, KV=KV, dk=dk, dv=dv, ps=ps, row_width=dk + dv,
-                                 k_off=0, v_off=dk, scale=scale, sink=to(sink), softcap=cap, dist_bias=to(dist))
-    keep = [params]      # the struct holds raw addresses: the tensors above stay alive through ``to`` results bound below
+    # the struct holds raw addresses: the device tensors stay bound to ``on`` until the kernels have run
+    on = {k: v.to(DEV) for k, v in dict(q=q, cache=cache, block_table=perm, tok_row=tok_row, tok_pos=tok_pos, row_q_start=q_start,
+                                        row_q_len=torch.tensor(lens, dtype=torch.int32), row_pos_start=torch.tensor(starts, dtype=torch.int32),
+                                        sink=sink, dist_bias=dist).items()}
+    params = ops.row_attn_params(q_stride=H * dk, q_head_stride=dk, out=out, H=H, KV=KV, dk=dk, dv=dv, ps=ps, row_width=dk + dv, k_off=0, v_off=dk,
+                                 scale=scale, softcap=cap, **on)
     if name == "float32":
         ops.attention_rows_plain(params)
     else:
@@ -426,13 +426,13 @@ def test_attention_kernels_with_a_cap_and_biases_by_distance(case):
             want = (e[:, None] * rows_kv[:, kv, dk:]).sum(0) / (e.sum() + math.exp(sink[h].item() - m))
             worst = max(worst, (got[t, h] - want).abs().max().item())
     assert worst <= (1e-5 if name == "float32" else 2e-2), worst
-    del keep
+    del on
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_small_kernels_of_the_feed_forwards_and_the_latent(dtype):
     """The gated activation with a cubic term (the tanh form of gelu), the norm of a slice of wider rows, the router's raw sigmoid
-    weights, and the rows an expert reads when a choice's weight multiplies its input."""
+    weights, and the experts' first product (and gathered rows) when a choice's weight multiplies what the expert reads."""
     from delta_b200.kernels import ops
     from delta_b200.parts.feed_forward import GELU_TANH_GATE, SILU_GATE
     g = torch.Generator().manual_seed(3)
@@ -460,10 +460,31 @@ def test_small_kernels_of_the_feed_forwards_and_the_latent(dtype):
     order = torch.sort(zz, dim=-1, descending=True).indices[:, :top]
     assert torch.equal(torch.sort(choice.cpu().long(), dim=-1).values, torch.sort(order, dim=-1).values)
     assert (weight.cpu().double() - torch.sigmoid(torch.gather(zz, 1, choice.cpu().long()))).abs().max().item() <= 1e-5
-    xs = torch.empty(T * top, d, dtype=dtype, device=DEV)
-    ops.experts_scale_rows(x.to(DEV), weight, xs)
-    want = (weight.cpu().double()[:, :, None] * x.double()[:, None, :]).view(T * top, d)
-    assert (xs.cpu().double() - want).abs().max().item() <= tol * want.abs().max().item()
+    # the experts' first product with a weight per slot: expert(w x) = act(w (x W^T)), the rows sorted by expert into tiles
+    F_ = 16
+    w1 = (torch.randn(E, 2 * F_, d, generator=g) * 0.3).to(dtype)
+    tile = ops.experts_tile_rows()
+    slots = T * top
+    capacity = -(-(slots + (tile - 1) * min(E, slots)) // tile) * tile
+    sorted_slots = torch.empty(capacity, dtype=torch.int32, device=DEV)
+    tile_expert = torch.empty(capacity // tile, dtype=torch.int32, device=DEV)
+    ops.experts_align(choice, E, sorted_slots, tile_expert, tile)
+    y = torch.zeros(capacity, F_, dtype=dtype, device=DEV)
+    ops.experts_gemm(x.to(DEV), w1.to(DEV), y, sorted_slots, tile_expert, top=top, n=F_, k=d, act="gated", limit=-1.0, alpha=1.0, shift=0.0,
+                     row_scale=weight.view(-1))
+    at = sorted_slots.cpu().tolist()
+    for p_, s_ in enumerate(at):
+        if s_ < 0:
+            continue
+        t_, e_ = s_ // top, int(choice.view(-1)[s_])
+        gu = (weight.view(-1)[s_].item() * x[t_].double()) @ w1[e_].double().T
+        want = plain.silu(gu[:F_]) * gu[F_:]
+        assert (y[p_].cpu().double() - want).abs().max().item() <= 3 * tol * max(1.0, want.abs().max().item())
+    if dtype == torch.bfloat16:      # the rows gathered side by side for the tcgen05 product carry the weight themselves
+        rows = ops.experts_gather(x.to(DEV), sorted_slots, top, torch.empty(capacity, d, dtype=dtype, device=DEV), row_scale=weight.view(-1))
+        for p_, s_ in enumerate(at):
+            want = weight.view(-1)[s_].item() * x[s_ // top].double() if s_ >= 0 else torch.zeros(d, dtype=torch.float64)
+            assert (rows[p_].cpu().double() - want).abs().max().item() <= tol * max(1.0, want.abs().max().item())
 
 
 def test_ramp_scaled_rotary_table():
