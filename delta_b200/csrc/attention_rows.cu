@@ -7,7 +7,7 @@
 //
 //   s_j  = (q . k_j) * scale          for the visible keys  max(0, i - window + 1) <= j <= i
 //   s_j <- softcap * tanh(s_j / softcap)                      (softcap > 0)
-//   s_j <- s_j + dist_bias[min(i - j, dist_max)][h]           (a table of biases by distance, one column a head)
+//   s_j <- s_j + dist_bias[h][min(i - j, dist_max)]           (a table of biases by distance, one row a head)
 //   p_j  = exp(s_j) / (sum_j' exp(s_j') [+ exp(sink_h)])
 //   y    = sum_j p_j v_j
 #include "common.cuh"
@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(CH) attention_rows_plain_kernel(const DkRowAtt
           for (int i = 0; i < dk; ++i) d = fmaf(qs[i], to_f32<T>(kr[i]), d);
           s = d * p.scale;
           if (p.softcap > 0.f) s = p.softcap * tanhf(s / p.softcap);
-          if (p.dist_bias != nullptr) s += p.dist_bias[(size_t)min(pos - key, p.dist_max) * p.H + h];
+          if (p.dist_bias != nullptr) s += p.dist_bias[(size_t)h * (p.dist_max + 1) + min(pos - key, p.dist_max)];
           vo = (long long)(base + p.v_off);
         }
       }

@@ -24,6 +24,14 @@ constexpr float LOG2E = 1.4426950408889634f;
 
 __host__ __device__ inline int pad128(int bytes) { return (bytes + 127) / 128 * 128; }
 
+// tanh(t) = 1 - 2 / (1 + e^(2t)) through the exponential and reciprocal units, without a branch: exact at both ends (e^(2t) of 0
+// or infinity), absolute error about 3e-7 elsewhere, which a score made of bfloat16 queries and keys does not see.
+__device__ __forceinline__ float tanh_by_exp(float t) {
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t * (2.f * LOG2E)));
+  return 1.f - __fdividef(2.f, 1.f + e);
+}
+
 // part[((t*H + head) * splits + split) * (dv + 2)]: dv floats of O, then m (log2 units), then l
 // RM: 16-row tiles of query rows per warp.  With two, every key and value fragment that a warp fetches from shared memory
 // feeds two products, which is what bounds this kernel (it moves 512 bytes of fragments for every 2 x 4,096 FLOP product).
@@ -87,8 +95,10 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_mma_kernel(const Dk
   float o[RM][NT][4];
   float m_run[RM][2], l_run[RM][2];
   int pos_r[RM][2];     // positions of this thread's query rows: rows warp*WR + rm*16 + gq and + 8
-  int head_r[RM][2];    // and their heads
+  const float* bias_r[RM][2];   // and the rows of the bias table of their heads
+  bool live_r[RM][2];           // whether the tile has these rows at all
   const bool shaped = p.softcap > 0.f || p.dist_bias != nullptr;
+  const float inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
 #pragma unroll
   for (int rm = 0; rm < RM; ++rm) {
 #pragma unroll
@@ -97,8 +107,12 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_mma_kernel(const Dk
     l_run[rm][0] = l_run[rm][1] = 0.f;
     pos_r[rm][0] = pos_start + (m0 + min(warp * WR + rm * 16 + gq, nrows - 1)) / G;
     pos_r[rm][1] = pos_start + (m0 + min(warp * WR + rm * 16 + gq + 8, nrows - 1)) / G;
-    head_r[rm][0] = g * G + (m0 + min(warp * WR + rm * 16 + gq, nrows - 1)) % G;
-    head_r[rm][1] = g * G + (m0 + min(warp * WR + rm * 16 + gq + 8, nrows - 1)) % G;
+    live_r[rm][0] = warp * WR + rm * 16 + gq < nrows;
+    live_r[rm][1] = warp * WR + rm * 16 + gq + 8 < nrows;
+    const size_t head0 = g * G + (m0 + min(warp * WR + rm * 16 + gq, nrows - 1)) % G;
+    const size_t head1 = g * G + (m0 + min(warp * WR + rm * 16 + gq + 8, nrows - 1)) % G;
+    bias_r[rm][0] = p.dist_bias != nullptr ? p.dist_bias + head0 * (p.dist_max + 1) : nullptr;
+    bias_r[rm][1] = p.dist_bias != nullptr ? p.dist_bias + head1 * (p.dist_max + 1) : nullptr;
   }
   const float sc_log2 = p.scale * LOG2E;
   const int warp_first_pos = pos_start + (m0 + min(warp * WR, nrows - 1)) / G;
@@ -154,19 +168,21 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_mma_kernel(const Dk
           for (int c = 0; c < 2; ++c) {
             const int key = kt0 + j * 8 + 2 * tq + c;
             float v0, v1;
-            if (shaped) {      // capped scores and biases by distance: in natural units first
-              v0 = s[rm][j][c] * p.scale;
-              v1 = s[rm][j][2 + c] * p.scale;
-              if (p.softcap > 0.f) {
-                v0 = p.softcap * tanhf(v0 / p.softcap);
-                v1 = p.softcap * tanhf(v1 / p.softcap);
+            if (shaped) {      // capped scores and biases by distance: in natural units first; rows the tile does not have are left out
+              v0 = v1 = -INFINITY;
+              if (live_r[rm][0]) {
+                v0 = s[rm][j][c] * p.scale;
+                if (p.softcap > 0.f) v0 = p.softcap * tanh_by_exp(v0 * inv_cap);
+                // (a key behind the query is masked below: its huge unsigned distance takes the last entry)
+                if (p.dist_bias != nullptr) v0 += bias_r[rm][0][min((unsigned)(pos_r[rm][0] - key), (unsigned)p.dist_max)];
+                v0 *= LOG2E;
               }
-              if (p.dist_bias != nullptr) {
-                v0 += p.dist_bias[(size_t)min(max(pos_r[rm][0] - key, 0), p.dist_max) * p.H + head_r[rm][0]];
-                v1 += p.dist_bias[(size_t)min(max(pos_r[rm][1] - key, 0), p.dist_max) * p.H + head_r[rm][1]];
+              if (live_r[rm][1]) {
+                v1 = s[rm][j][2 + c] * p.scale;
+                if (p.softcap > 0.f) v1 = p.softcap * tanh_by_exp(v1 * inv_cap);
+                if (p.dist_bias != nullptr) v1 += bias_r[rm][1][min((unsigned)(pos_r[rm][1] - key), (unsigned)p.dist_max)];
+                v1 *= LOG2E;
               }
-              v0 *= LOG2E;
-              v1 *= LOG2E;
             } else {
               v0 = s[rm][j][c] * sc_log2;
               v1 = s[rm][j][2 + c] * sc_log2;

@@ -17,7 +17,7 @@ struct DkRowAttnParams {
   const int* row_q_len;     // [rows] tokens of the row in this step
   const int* row_pos_start; // [rows] position of the row's first token
   const float* sink;        // [H] a logit that joins every softmax denominator with no value; or null
-  const float* dist_bias;   // [dist_max + 1, H] added to the score of query i and key j: row min(i - j, dist_max); or null
+  const float* dist_bias;   // [H, dist_max + 1] added to the score of query i and key j: entry min(i - j, dist_max) of the head's row; or null
   void* scratch;            // partial results of kernels that split the keys; or null
   int* err;                 // device error record, 4 ints; or null
   int T, rows, H, KV, dk, dv, ps, max_pages, num_pages;
@@ -28,6 +28,6 @@ struct DkRowAttnParams {
   int row_filter;           // 0: every row; 1: only rows that bring one token; 2: only rows that bring more
   float scale;
   float softcap;            // > 0: the scaled score s becomes softcap * tanh(s / softcap) (before the distance bias)
-  int dist_max;             // last row of dist_bias: every distance from here on takes it
+  int dist_max;             // last entry of a row of dist_bias: every distance from here on takes it
   int reserved;
 };

@@ -524,8 +524,8 @@ RowAttnParams = _l.RowAttnParams
 def row_attn_params(*, q, q_stride, q_head_stride, out, cache, block_table, tok_row, tok_pos, row_q_start, row_q_len,
                     row_pos_start, H, KV, dk, dv, ps, row_width, k_off, v_off, scale, window=0, sink=None, softcap=None, dist_bias=None,
                     err=None) -> RowAttnParams:
-    """``softcap`` c: the scaled score s becomes c tanh(s / c).  ``dist_bias`` float32 [D + 1, H]: row min(i - j, D) is added to the
-    scores of query i and key j, one column a head (after the cap; the scale does not multiply it)."""
+    """``softcap`` c: the scaled score s becomes c tanh(s / c).  ``dist_bias`` float32 [H, D + 1]: entry min(i - j, D) of a head's row
+    is added to the scores of query i and key j (after the cap; the scale does not multiply it)."""
     i32 = torch.int32
     if tuple(cache.shape[1:]) != (KV, ps, row_width) or cache.dtype != q.dtype:
         raise KernelError(f"attention_rows: cache has shape {tuple(cache.shape)} / {cache.dtype}, expected [pages, {KV}, {ps}, {row_width}] of {q.dtype}")
@@ -537,9 +537,9 @@ def row_attn_params(*, q, q_stride, q_head_stride, out, cache, block_table, tok_
     p.row_pos_start = _ptr(row_pos_start, "row_pos_start", i32)
     p.sink = _ptr(sink, "sink", torch.float32)
     if dist_bias is not None:
-        if dist_bias.dim() != 2 or dist_bias.shape[1] != H or dist_bias.shape[0] < 1:
-            raise KernelError(f"attention_rows: the distance biases have shape {tuple(dist_bias.shape)}, expected [distances, {H}]")
-        p.dist_bias, p.dist_max = _ptr(dist_bias, "dist_bias", torch.float32), dist_bias.shape[0] - 1
+        if dist_bias.dim() != 2 or dist_bias.shape[0] != H or dist_bias.shape[1] < 1:
+            raise KernelError(f"attention_rows: the distance biases have shape {tuple(dist_bias.shape)}, expected [{H}, distances]")
+        p.dist_bias, p.dist_max = _ptr(dist_bias, "dist_bias", torch.float32), dist_bias.shape[1] - 1
     p.softcap = float(softcap or 0.0)
     p.err = _ptr(err, "err", i32)
     p.T, p.rows = tok_row.shape[0], block_table.shape[0]

@@ -45,6 +45,7 @@ from .base import MIXERS, PAGE, POSITION_ENCODINGS, CacheSpec, Mixer, PartSpec, 
 
 
 MAX_SPLITS = 32
+SINGLE_WARP_BLOCKS_PER_SM = 6      # blocks of one warp (a tile of a single token's heads) that an SM holds at a time
 PARTIALS = "row_attention.partials"
 
 
@@ -53,12 +54,13 @@ def plain(ctx) -> bool:
 
 
 def decode_splits(rows: int, kv_heads: int, group: int, max_keys: int, sm_count: int) -> int:
-    """Blocks that share the keys of a (row, key-value head) in a step of single tokens: enough to fill the device about
-    twice, and so few that every block has two key tiles."""
+    """Blocks that share the keys of a (row, key-value head) in a step of single tokens: enough to fill the device (a group of
+    up to 16 heads is one warp a block, of which an SM holds about six; larger groups take four warps a block, two blocks an SM),
+    and so few that every block has two key tiles."""
     small = group <= 16
     blocks = max(1, rows * kv_heads * (1 if small else -(-group // 64)))
     tiles = max(1, -(-max_keys // (32 if small else 64)))
-    return max(1, min(2 * sm_count // blocks, tiles // 2, MAX_SPLITS))
+    return max(1, min((SINGLE_WARP_BLOCKS_PER_SM if small else 2) * sm_count // blocks, tiles // 2, MAX_SPLITS))
 
 
 def run(ctx, params) -> None:
@@ -215,10 +217,10 @@ class SinkAttention(Mixer):
         self.sink = tensors[p + n["sink"]].float().contiguous() if self.has_sink else None
         if self.sink_logit is not None:
             self.sink = torch.full((self.heads,), self.sink_logit, dtype=torch.float32, device=self.w_o.device)
-        if self.distance_bias:      # the table by bucket, spread out by distance: row min(i - j, last) of [last + 1, heads]
+        if self.distance_bias:      # the table by bucket, spread out by distance, a row a head: entry min(i - j, last) of [heads, last + 1]
             rel = tensors[p + n["rel"]].float()
             buckets = torch.tensor(distance_buckets(**self.distance_bias), dtype=torch.long, device=rel.device)
-            self.dist_table = rel[buckets].contiguous()
+            self.dist_table = rel[buckets].t().contiguous()
 
     def cache_spec(self):
         # a page of a layer: [kv head][offset in the page][key | value]

@@ -395,7 +395,7 @@ def test_attention_kernels_with_a_cap_and_biases_by_distance(case):
     # the struct holds raw addresses: the device tensors stay bound to ``on`` until the kernels have run
     on = {k: v.to(DEV) for k, v in dict(q=q, cache=cache, block_table=perm, tok_row=tok_row, tok_pos=tok_pos, row_q_start=q_start,
                                         row_q_len=torch.tensor(lens, dtype=torch.int32), row_pos_start=torch.tensor(starts, dtype=torch.int32),
-                                        sink=sink, dist_bias=dist).items()}
+                                        sink=sink, dist_bias=dist.t().contiguous()).items()}
     params = ops.row_attn_params(q_stride=H * dk, q_head_stride=dk, out=out, H=H, KV=KV, dk=dk, dv=dv, ps=ps, row_width=dk + dv, k_off=0, v_off=dk,
                                  scale=scale, softcap=cap, **on)
     if name == "float32":
