@@ -35,7 +35,8 @@ __device__ __forceinline__ float tanh_by_exp(float t) {
 // part[((t*H + head) * splits + split) * (dv + 2)]: dv floats of O, then m (log2 units), then l
 // RM: 16-row tiles of query rows per warp.  With two, every key and value fragment that a warp fetches from shared memory
 // feeds two products, which is what bounds this kernel (it moves 512 bytes of fragments for every 2 x 4,096 FLOP product).
-template <int WARPS, int KT, int DVMAX, int RM>
+// SHAPED: scores are capped and take biases by distance (an instance of its own, so that the others keep their registers).
+template <int WARPS, int KT, int DVMAX, int RM, bool SHAPED>
 __global__ void __launch_bounds__(WARPS * 32) attention_rows_mma_kernel(const DkRowAttnParams p, float* __restrict__ part) {
   constexpr int QT = 16 * WARPS * RM, THREADS = WARPS * 32, NT = DVMAX / 8, WR = 16 * RM;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -97,8 +98,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_mma_kernel(const Dk
   int pos_r[RM][2];     // positions of this thread's query rows: rows warp*WR + rm*16 + gq and + 8
   const float* bias_r[RM][2];   // and the rows of the bias table of their heads
   bool live_r[RM][2];           // whether the tile has these rows at all
-  const bool shaped = p.softcap > 0.f || p.dist_bias != nullptr;
-  const float inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
+  const float inv_cap = (SHAPED && p.softcap > 0.f) ? 1.f / p.softcap : 0.f;
 #pragma unroll
   for (int rm = 0; rm < RM; ++rm) {
 #pragma unroll
@@ -107,12 +107,14 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_mma_kernel(const Dk
     l_run[rm][0] = l_run[rm][1] = 0.f;
     pos_r[rm][0] = pos_start + (m0 + min(warp * WR + rm * 16 + gq, nrows - 1)) / G;
     pos_r[rm][1] = pos_start + (m0 + min(warp * WR + rm * 16 + gq + 8, nrows - 1)) / G;
-    live_r[rm][0] = warp * WR + rm * 16 + gq < nrows;
-    live_r[rm][1] = warp * WR + rm * 16 + gq + 8 < nrows;
-    const size_t head0 = g * G + (m0 + min(warp * WR + rm * 16 + gq, nrows - 1)) % G;
-    const size_t head1 = g * G + (m0 + min(warp * WR + rm * 16 + gq + 8, nrows - 1)) % G;
-    bias_r[rm][0] = p.dist_bias != nullptr ? p.dist_bias + head0 * (p.dist_max + 1) : nullptr;
-    bias_r[rm][1] = p.dist_bias != nullptr ? p.dist_bias + head1 * (p.dist_max + 1) : nullptr;
+    if constexpr (SHAPED) {
+      live_r[rm][0] = warp * WR + rm * 16 + gq < nrows;
+      live_r[rm][1] = warp * WR + rm * 16 + gq + 8 < nrows;
+      const size_t head0 = g * G + (m0 + min(warp * WR + rm * 16 + gq, nrows - 1)) % G;
+      const size_t head1 = g * G + (m0 + min(warp * WR + rm * 16 + gq + 8, nrows - 1)) % G;
+      bias_r[rm][0] = p.dist_bias != nullptr ? p.dist_bias + head0 * (p.dist_max + 1) : nullptr;
+      bias_r[rm][1] = p.dist_bias != nullptr ? p.dist_bias + head1 * (p.dist_max + 1) : nullptr;
+    }
   }
   const float sc_log2 = p.scale * LOG2E;
   const int warp_first_pos = pos_start + (m0 + min(warp * WR, nrows - 1)) / G;
@@ -168,7 +170,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_mma_kernel(const Dk
           for (int c = 0; c < 2; ++c) {
             const int key = kt0 + j * 8 + 2 * tq + c;
             float v0, v1;
-            if (shaped) {      // capped scores and biases by distance: in natural units first; rows the tile does not have are left out
+            if constexpr (SHAPED) {      // capped scores and biases by distance: in natural units first; rows the tile does not have are left out
               v0 = v1 = -INFINITY;
               if (live_r[rm][0]) {
                 v0 = s[rm][j][c] * p.scale;
@@ -330,8 +332,8 @@ __global__ void attention_rows_merge_kernel(const DkRowAttnParams p, const float
   }
 }
 
-template <int WARPS, int KT, int DVMAX, int RM>
-int launch(const DkRowAttnParams& p, int max_m, int splits, float* part, cudaStream_t stream) {
+template <int WARPS, int KT, int DVMAX, int RM, bool SHAPED>
+int launch_as(const DkRowAttnParams& p, int max_m, int splits, float* part, cudaStream_t stream) {
   const int m_tiles = (max_m + 16 * WARPS * RM - 1) / (16 * WARPS * RM);
   const size_t smem = (size_t)16 * WARPS * RM * pad128(p.dk * 2) + (size_t)PSTAGES * KT * pad128(p.row_width * 2);
   if (smem > 220 * 1024) {
@@ -341,7 +343,7 @@ int launch(const DkRowAttnParams& p, int max_m, int splits, float* part, cudaStr
   static size_t configured_on[DK_MAX_DEVICES] = {0};
   size_t& configured = configured_on[dk_current_device()];
   if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_rows_mma_kernel<WARPS, KT, DVMAX, RM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_rows_mma_kernel<WARPS, KT, DVMAX, RM, SHAPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) {
       dk_set_error("attention_rows_mma: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
       return DK_ERR_LAUNCH;
@@ -349,8 +351,15 @@ int launch(const DkRowAttnParams& p, int max_m, int splits, float* part, cudaStr
     configured = smem;
   }
   dim3 grid(m_tiles, splits, p.rows * p.KV);
-  attention_rows_mma_kernel<WARPS, KT, DVMAX, RM><<<grid, WARPS * 32, smem, stream>>>(p, part);
+  attention_rows_mma_kernel<WARPS, KT, DVMAX, RM, SHAPED><<<grid, WARPS * 32, smem, stream>>>(p, part);
   return dk_check_launch("attention_rows_mma");
+}
+
+// RM_SHAPED: the 16-row tiles a warp takes when the scores are shaped (the shaping's registers leave room for fewer).
+template <int WARPS, int KT, int DVMAX, int RM, int RM_SHAPED = RM>
+int launch(const DkRowAttnParams& p, int max_m, int splits, float* part, cudaStream_t stream) {
+  if (p.softcap > 0.f || p.dist_bias != nullptr) return launch_as<WARPS, KT, DVMAX, RM_SHAPED, true>(p, max_m, splits, part, stream);
+  return launch_as<WARPS, KT, DVMAX, RM, false>(p, max_m, splits, part, stream);
 }
 }  // namespace
 
@@ -394,7 +403,11 @@ extern "C" int dk_attention_rows_mma(const DkRowAttnParams* pp, int max_m, int s
   } else if (max_m <= 64) {
     e = p.dv <= 64 ? launch<4, 64, 64, 1>(p, max_m, splits, part, stream) : launch<4, 64, 128, 1>(p, max_m, splits, part, stream);
   } else {
-    e = p.dv <= 64 ? launch<4, 64, 64, 2>(p, max_m, splits, part, stream) : launch<4, 64, 128, 2>(p, max_m, splits, part, stream);
+    // (shaped scores with a value of 128: two tiles a warp spill 224 bytes; one tile a warp was measured against them)
+    // Shaped scores with a value of 128: two tiles a warp spill 224 bytes.  Measured (16 heads on 4, key and value 128, 2,048
+    // tokens, a layer): 4 warps x 2 tiles 0.69 ms, 4 warps x 1 tile 0.57, 8 warps x 1 tile on a shared key tile 0.49.
+    if (p.dv > 64 && (p.softcap > 0.f || p.dist_bias != nullptr)) e = launch_as<8, 64, 128, 1, true>(p, max_m, splits, part, stream);
+    else e = p.dv <= 64 ? launch<4, 64, 64, 2>(p, max_m, splits, part, stream) : launch<4, 64, 128, 2>(p, max_m, splits, part, stream);
   }
   if (e != 0 || splits == 1) return e;
   DK_REQUIRE(p.H <= 65535, "attention_rows_mma: too many heads");
