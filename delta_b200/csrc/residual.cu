@@ -22,7 +22,7 @@ __global__ void embedding_pair_kernel(const int* __restrict__ tokens, const int*
                                       const int* __restrict__ row_q_start, const int* __restrict__ row_slot,
                                       const int* __restrict__ prev_state, const T* __restrict__ table, float scale,
                                       const T* __restrict__ pair_table, long long buckets, long long mul_prev, long long mul_cur,
-                                      float* __restrict__ X, float* __restrict__ E, int d, int vocab, int* err) {
+                                      float* __restrict__ X, float* __restrict__ E, T* __restrict__ R, int d, int vocab, int* err) {
   const int t = blockIdx.x;
   const int tok = tokens[t];
   const bool bad = tok < 0 || tok >= vocab;
@@ -45,6 +45,7 @@ __global__ void embedding_pair_kernel(const int* __restrict__ tokens, const int*
     if (pair != nullptr) v += to_f32<T>(pair[i]);
     X[(size_t)t * d + i] = v;
     if (E != nullptr) E[(size_t)t * d + i] = v;
+    if (R != nullptr) R[(size_t)t * d + i] = from_f32<T>(v);      // the stream in the compute type, for a first sublayer that reads it
   }
 }
 
@@ -182,7 +183,7 @@ extern "C" int dk_normed_sum(const float* y1, const float* b1, const float* w1, 
 
 extern "C" int dk_embedding_pair(const int* tokens, const int* tok_row, const int* tok_pos, const int* row_q_start, const int* row_slot,
                                  int* prev_state, const void* table, float scale, const void* pair_table, long long buckets,
-                                 long long mul_prev, long long mul_cur, float* X, float* E, int T_, int d, int vocab, int dtype, int* err,
+                                 long long mul_prev, long long mul_cur, float* X, float* E, void* R, int T_, int d, int vocab, int dtype, int* err,
                                  cudaStream_t stream) {
   if (T_ == 0) return 0;
   DK_REQUIRE(T_ > 0 && d > 0 && vocab > 0, "embedding_pair: bad sizes T=%d d=%d vocab=%d", T_, d, vocab);
@@ -190,7 +191,7 @@ extern "C" int dk_embedding_pair(const int* tokens, const int* tok_row, const in
   const int threads = d >= 1024 ? 256 : 128;
 #define LAUNCH(T)                                                                                                               \
   embedding_pair_kernel<T><<<T_, threads, 0, stream>>>(tokens, tok_row, tok_pos, row_q_start, row_slot, prev_state, (const T*)table, \
-                                                        scale, (const T*)pair_table, buckets, mul_prev, mul_cur, X, E, d, vocab, err)
+                                                        scale, (const T*)pair_table, buckets, mul_prev, mul_cur, X, E, (T*)R, d, vocab, err)
   if (dtype == DK_F32) LAUNCH(float);
   else if (dtype == DK_BF16) LAUNCH(__nv_bfloat16);
   else DK_REQUIRE(false, "embedding_pair: unknown dtype %d", dtype);

@@ -89,7 +89,7 @@ _SIGNATURES = {
     "dk_gemm_stream_k_supported": [I, I, I, I],
     "dk_gemm_stream_k": [P, P, P, I, I, I, I, I, I, I, I, P, P, P],
     "dk_wait_check": [P, C.c_longlong, P],
-    "dk_embedding_pair": [P, P, P, P, P, P, P, F, P, L, L, L, P, P, I, I, I, I, P, P],
+    "dk_embedding_pair": [P, P, P, P, P, P, P, F, P, L, L, L, P, P, P, I, I, I, I, P, P],
     "dk_remember_tokens": [P, P, P, P, P, I, P],
     "dk_residual_norm": [P, P, P, P, P, P, P, P, P, I, I, F, I, I, I, I, P],
     "dk_sublayer_norm_add": [P, P, P, P, P, I, I, F, I, I, I, P],

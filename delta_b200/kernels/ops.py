@@ -655,17 +655,17 @@ NORM_KINDS = {"rms": 0, "layer": 1}
 
 
 def embedding_pair(tokens, table, X, *, scale=1.0, pair_table=None, buckets=0, mul_prev=0, mul_cur=0, prev_state=None, tok_row=None,
-                   tok_pos=None, row_q_start=None, row_slot=None, keep=None, err=None):
+                   tok_pos=None, row_q_start=None, row_slot=None, keep=None, rounded=None, err=None):
     """X[t] = table[tokens[t]] * scale (+ pair_table[(previous token * mul_prev + token * mul_cur) mod buckets]; a request's
     first token takes row ``buckets``; the token before a portion's first comes from ``prev_state`` [slots, 1]).  X, and
-    ``keep`` when given (a second copy), are float32 [T, d]."""
+    ``keep`` when given (a second copy), are float32 [T, d]; ``rounded`` when given takes X in the table's type."""
     T, d = X.shape
     i32 = torch.int32
     _l.check(_l.load().dk_embedding_pair(
         _ptr(tokens, "tokens", i32), _ptr(tok_row, "tok_row", i32), _ptr(tok_pos, "tok_pos", i32), _ptr(row_q_start, "row_q_start", i32),
         _ptr(row_slot, "row_slot", i32), _ptr(prev_state, "prev_state", i32), _ptr(table, "table"), float(scale),
         _ptr(pair_table, "pair_table", table.dtype), int(buckets), int(mul_prev), int(mul_cur), _ptr(X, "X", torch.float32),
-        _ptr(keep, "keep", torch.float32), T, d, table.shape[0], dtype_code(table.dtype), _ptr(err, "err", i32), _stream()), "embedding_pair")
+        _ptr(keep, "keep", torch.float32), _ptr(rounded, "rounded", table.dtype), T, d, table.shape[0], dtype_code(table.dtype), _ptr(err, "err", i32), _stream()), "embedding_pair")
     return X
 
 

@@ -80,4 +80,4 @@ def mevulix_spec(cfg: MevulixConfig, engine: Optional[EngineConfig] = None) -> M
     return ModelSpec(
         vocab_size=cfg.vocab, width=d, layers=tuple(layers), order=order, final_norm=norm("final.norm"),
         embedding=TensorSpec("embed", (cfg.vocab, d), kind="table"), lm_head=TensorSpec("head", (cfg.vocab, d), kind="matrix"),
-        max_positions=engine.max_seq_len, stream=PartSpec("residual_f32", dict(width=d), "stream"), logit_scale=cfg.logit_scale)
+        max_positions=engine.max_seq_len, stream=PartSpec("residual_f32", dict(width=d, rounded_start=True), "stream"), logit_scale=cfg.logit_scale)

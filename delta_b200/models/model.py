@@ -105,7 +105,7 @@ class Model:
         x = self.stream.start(ctx, self.embed_table)
         for p in self.parts():
             p.begin_step(ctx)
-        pending = None
+        pending = self.stream.initial_pending()
         totals = ctx.capture.get("layer_totals") if ctx.capture is not None else None
         for e in self.order:
             block = self.blocks[e.layer]

@@ -209,6 +209,10 @@ class Stream(Part):
     def start(self, ctx, table):
         raise NotImplementedError
 
+    def initial_pending(self):
+        """What the first block gets as ``pending`` (None: nothing is pending after ``start``)."""
+        return None
+
     def enter_pass(self, ctx, x, pending, number: int):
         """Called before the first layer of pass ``number`` of a span of layers that runs several times; returns
         (x, pending).  Streams of models without such a span never see it."""

@@ -70,9 +70,14 @@ def read(ctx, x, pending: Optional[Pending], norm, rows=None, write_back=True):
 
 @STREAMS.register("residual_f32")
 class ResidualStream(Stream):
-    def __init__(self, width: int, scale: float = 1.0, pair: Optional[dict] = None, reentry: Optional[dict] = None):
+    def __init__(self, width: int, scale: float = 1.0, pair: Optional[dict] = None, reentry: Optional[dict] = None,
+                 rounded_start: bool = False):
         """``pair``: {name, buckets, mul_prev, mul_cur} of the hashed pair table [buckets + 1, d] (None: none).
-        ``reentry``: {name, passes, add_embedding}, or {project, passes} (None: no span runs more than once)."""
+        ``reentry``: {name, passes, add_embedding}, or {project, passes} (None: no span runs more than once).
+        ``rounded_start``: the embedding kernel also leaves the stream in the compute type and ``initial_pending`` hands it to the
+        first block (for blocks whose sublayers read the stream itself)."""
+        self.rounded_start = bool(rounded_start)
+        self._rounded = None
         self.width, self.scale = int(width), float(scale)
         self.pair = dict(pair) if pair else None
         self.reentry = dict(reentry) if reentry else None
@@ -114,14 +119,20 @@ class ResidualStream(Stream):
             keep = ctx.scratch(KEPT, (T, self.width), torch.float32, bound=(ctx.max_step_tokens, self.width))
         pair = self.pair or {}
         state = ctx.state(PREV_TOKEN) if self.pair else None
+        self._rounded = None
+        if self.rounded_start and ctx.dtype != torch.float32:
+            self._rounded = torch.empty((T, self.width), dtype=ctx.dtype, device=ctx.device)
         ops.embedding_pair(ctx.tokens, table, x, scale=self.scale, pair_table=self.pair_table, buckets=pair.get("buckets", 0),
                            mul_prev=pair.get("mul_prev", 0), mul_cur=pair.get("mul_cur", 0), prev_state=state, tok_row=ctx.tok_row,
-                           tok_pos=ctx.tok_pos, row_q_start=ctx.row_q_start, row_slot=ctx.row_slot, keep=keep, err=ctx.err)
+                           tok_pos=ctx.tok_pos, row_q_start=ctx.row_q_start, row_slot=ctx.row_slot, keep=keep, rounded=self._rounded, err=ctx.err)
         if self.pair:
             ops.remember_tokens(ctx.tokens, state, row_q_start=ctx.row_q_start, row_q_len=ctx.row_q_len, row_slot=ctx.row_slot)
         self._kept = keep
         self._projected = None
         return x
+
+    def initial_pending(self):
+        return Pending(rounded=self._rounded) if self._rounded is not None else None
 
     def _enter_projected(self, ctx, x, pending):
         """x <- A x + B x0: the settled stream goes through A here, B x0 (made once per step) is left pending."""
