@@ -612,7 +612,7 @@ def design_workload(args, design: str) -> int:
                 "sublayer_norm_add": ((2 * d * 4 + 2 * d * 2) * T * (2 * runs), 0),
                 "residual_norm": ((d * 4 + d * 2) * T, 0),
                 "rms_norm_strided": (2 * Rq * 2 * T * n_lat, 0),
-                "latent_prepare": ((2 * H * 64 + 2 * 320) * 2 * T * n_lat, 0),
+                "latent_prepare": ((H * 192 + 320 + 320 + H * 64) * 2 * T * n_lat, 0),      # counted as in the Roletar table: the whole query row
                 "rows_append_unit": (((2 * H + 4 * G) * n_own + 2 * H * (n_att - n_own)) * 128 * 2 * T, 0),
                 "glu_clamped": (3 * (Fd * n_dense + F * n_moe) * 2 * T, 0),
                 "experts_scale_rows": ((1 + top) * d * 2 * T * n_moe, 0),
