@@ -229,6 +229,58 @@ extern "C" int dk_residual_norm(float* X, const void* y1, const void* y2, const 
   return dk_check_launch("residual_norm");
 }
 
+// The same for a width that is a multiple of 8 with 16-byte aligned rows: a thread keeps V groups of eight entries of y and of
+// x in registers from the start, so every load of the block is under way before the first sum is needed, and nothing is staged
+// in shared memory.
+template <typename T, typename TO, int V>
+__global__ void sublayer_norm_add_vec_kernel(float* __restrict__ X, const T* __restrict__ y, const float* __restrict__ w,
+                                             const float* __restrict__ b, TO* __restrict__ out, int d, float eps, int kind) {
+  __shared__ float scratch[34];
+  const size_t at = (size_t)blockIdx.x * d;
+  const int groups = d / 8;
+  float yv[V][8], xv[V][8];
+  float sum = 0.f;
+#pragma unroll
+  for (int v = 0; v < V; ++v) {
+    const int c = threadIdx.x + v * blockDim.x;
+    if (c < groups) {
+      load8<T>(y + at + (size_t)c * 8, yv[v]);
+      load8<float>(X + at + (size_t)c * 8, xv[v]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sum += yv[v][e];
+    }
+  }
+  float mean = 0.f;
+  if (kind == 1) mean = block_sum(sum, scratch) / (float)d;
+  float ss = 0.f;
+#pragma unroll
+  for (int v = 0; v < V; ++v) {
+    const int c = threadIdx.x + v * blockDim.x;
+    if (c < groups) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        yv[v][e] -= mean;
+        ss += yv[v][e] * yv[v][e];
+      }
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.f / sqrtf(ss / (float)d + eps);
+#pragma unroll
+  for (int v = 0; v < V; ++v) {
+    const int c = threadIdx.x + v * blockDim.x;
+    if (c < groups) {
+      float wv[8], bv[8];
+      load8<float>(w + (size_t)c * 8, wv);
+      if (b != nullptr) load8<float>(b + (size_t)c * 8, bv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) xv[v][e] += yv[v][e] * inv * wv[e] + (b != nullptr ? bv[e] : 0.f);
+      store8<float>(X + at + (size_t)c * 8, xv[v]);
+      if (out != nullptr) store8<TO>(out + at + (size_t)c * 8, xv[v]);
+    }
+  }
+}
+
 extern "C" int dk_sublayer_norm_add(float* X, const void* y, const float* w, const float* b, void* out, int T_, int d,
                                     float eps, int kind, int y_dtype, int out_dtype, cudaStream_t stream) {
   if (T_ == 0) return 0;
@@ -238,7 +290,16 @@ extern "C" int dk_sublayer_norm_add(float* X, const void* y, const float* w, con
   DK_REQUIRE(w != nullptr, "sublayer_norm_add: the norm has no weight");
   const int threads = d >= 4096 ? 512 : (d >= 1024 ? 256 : 128);
   const size_t smem = (size_t)(d + 36) * sizeof(float);
-#define LAUNCH(T, TO) sublayer_norm_add_kernel<T, TO><<<T_, threads, smem, stream>>>(X, (const T*)y, w, b, (TO*)out, d, eps, kind)
+  auto aligned = [](const void* q) { return q == nullptr || ((uintptr_t)q % 16) == 0; };
+  const int groups = d / 8;
+  const bool vec = d % 8 == 0 && groups <= 2048 && aligned(X) && aligned(y) && aligned(w) && aligned(b) && aligned(out);
+  const int vthreads = groups <= 1024 ? (groups + 31) / 32 * 32 : 1024;      // one group of eight a thread up to a width of 8,192, then two
+#define LAUNCH(T, TO)                                                                                                             \
+  do {                                                                                                                            \
+    if (vec && groups <= 1024) sublayer_norm_add_vec_kernel<T, TO, 1><<<T_, vthreads, 0, stream>>>(X, (const T*)y, w, b, (TO*)out, d, eps, kind); \
+    else if (vec) sublayer_norm_add_vec_kernel<T, TO, 2><<<T_, vthreads, 0, stream>>>(X, (const T*)y, w, b, (TO*)out, d, eps, kind); \
+    else sublayer_norm_add_kernel<T, TO><<<T_, threads, smem, stream>>>(X, (const T*)y, w, b, (TO*)out, d, eps, kind);           \
+  } while (0)
   if (y_dtype == DK_F32 && out_dtype == DK_F32) LAUNCH(float, float);
   else if (y_dtype == DK_BF16 && out_dtype == DK_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
   else if (y_dtype == DK_BF16 && out_dtype == DK_F32) LAUNCH(__nv_bfloat16, float);

@@ -304,7 +304,7 @@ DEV = "cuda:0"
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("d", [50, 256, 1030])
+@pytest.mark.parametrize("d", [50, 256, 1030, 2048, 9000])
 @pytest.mark.parametrize("kind", ["layer", "rms"])
 def test_sublayer_norm_add_kernel(dtype, d, kind):
     from delta_b200.kernels import ops
